@@ -18,7 +18,7 @@ kbench)
   echo "kbench rc=$?"
   grep -E "prefill|fa2_varlen" gpurun_out/r02_kbench.jsonl ;;
 ncu)
-  timeout 600 ncu --set full --clock-control none --import-source on \
+  timeout 600 ncu --set full --clock-control none \
     -k regex:prefill_umma_kernel -s 4 -c 1 -f -o gpurun_out/r02_prefill_umma python tools/kbench.py prefill16 \
     > gpurun_out/r02_ncu_prefill.log 2>&1
   echo "ncu prefill rc=$?" ;;
