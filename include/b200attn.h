@@ -38,6 +38,7 @@ typedef void* b200_stream_t; /* cudaStream_t */
 enum {
   B200_DTYPE_BF16 = 0,
   B200_DTYPE_F16 = 1,
+  B200_DTYPE_F32 = 2,            /* the sequence-mixer kernels (b200_attn_generic ... b200_act_and_mul) only */
 };
 
 enum {
@@ -404,6 +405,73 @@ int b200_comm_free(void* ptr);
 int b200_comm_get_handle(const void* ptr, void* handle64);
 int b200_comm_open_handle(const void* handle64, void** ptr);
 int b200_comm_close_handle(void* ptr);
+
+/* ---------------------------------------------------------------------------------------------------
+ * Sequence-mixer kernels of the hybrid decoders (csrc/seq_ops.cu, csrc/seq_mixers.cu). dtype may also be
+ * B200_DTYPE_F32 (every activation in true 32-bit). Small parameters (norm weights, taps, decays, biases
+ * of the step size) are fp32 whatever the dtype. Which tokens belong to which sequence is given in one of
+ * two forms: packed spans cu_q / cu_k (int32 [num_seqs + 1]; sequence s owns tokens cu_q[s] .. cu_q[s+1]
+ * and sees cu_k[s+1] - cu_k[s] keys, its own tokens last) or, with cu_q == NULL, ctx_lens (int32
+ * [num_seqs]; sequence s owns token s and sees ctx_lens[s] keys; 0 marks a padded row that is skipped).
+ * A span whose first position is 0 starts from a zero state whatever its slot holds. */
+
+/* h = r * rsqrt(mean(r^2) + eps) * (offset + w); r fp32 [rows, hidden], h in dtype. */
+int b200_residual_rmsnorm(void* out, const float* residual, const float* weight, float offset, float eps,
+                          int32_t rows, int32_t hidden, int32_t dtype, b200_stream_t stream);
+
+/* r += norm(y; w_post) (fp32, in place); h = norm(r; w_pre) in dtype (skipped when w_pre == NULL). */
+int b200_residual_add_norms(void* h, float* residual, const void* y, const float* w_post,
+                            const float* w_pre, float offset, float eps, int32_t rows, int32_t hidden,
+                            int32_t dtype, b200_stream_t stream);
+
+/* Depth-wise causal convolution over time: out[t, c] = act(bias[c] + sum_j w[c, j] x[t - taps + 1 + j, c]),
+ * zeros before a sequence's start; state [slots, taps - 1, channels] (dtype) carries each sequence's last
+ * taps - 1 inputs between steps. act: 0 none, 1 silu. taps <= 8. out must not alias x. */
+int b200_causal_conv(void* out, int64_t out_stride, const void* x, int64_t x_stride, const float* weight,
+                     const float* bias, int32_t act, void* state, const int32_t* state_slots,
+                     const int32_t* cu_q, const int32_t* cu_k, const int32_t* ctx_lens, int32_t num_seqs,
+                     int32_t max_q, int32_t channels, int32_t taps, int32_t dtype, b200_stream_t stream);
+
+/* In place on qkv [T, H*dim | G*dim | G*vdim]: q and k heads divided by their root mean square (eps inside
+ * the root), q times 1 + coef * ln(floor((pos + 1) / every) + 1); k and v rows stored at `slots` (flat, or
+ * (block, offset) pairs) of the caches [nb, bs, G*dim] / [nb, bs, G*vdim] when those are given. */
+int b200_unitnorm_temp_cache(void* qkv, int64_t stride, const int64_t* positions, float eps, float coef,
+                             int32_t every, void* k_cache, void* v_cache, const int32_t* slots,
+                             int32_t slot_pairs, int32_t block_size, int32_t num_tokens, int32_t num_heads,
+                             int32_t num_kv_heads, int32_t dim, int32_t vdim, int32_t dtype,
+                             b200_stream_t stream);
+
+/* out = gate-and-norm of y [rows, n] (fp32 when y_is_f32, else dtype) with gate [rows, n] (dtype, row
+ * stride): RMS norm over each of `groups` equal parts times weight, the gate act(g) (0 sigmoid, 1 silu)
+ * applied before the norm (gate_first) or after it; weight == NULL: the gate alone. */
+int b200_gated_norm(void* out, const void* y, int32_t y_is_f32, const void* gate, int64_t gate_stride,
+                    const float* weight, float eps, int32_t rows, int32_t n, int32_t groups,
+                    int32_t gate_first, int32_t gate_act, int32_t dtype, b200_stream_t stream);
+
+/* out[r, i] = act(x[r, i]) * x[r, inter + i]; act: 0 silu, 1 relu, 2 gelu (tanh form). */
+int b200_act_and_mul(void* out, const void* x, int32_t rows, int32_t inter, int32_t act, int32_t dtype,
+                     b200_stream_t stream);
+
+/* Causal softmax attention for any key size `dim` and value size `vdim` (<= 256), packed keys
+ * (block_tables == NULL: k, v are this step's rows in the order of cu_k) or paged caches
+ * [nb, bs, G*dim] / [nb, bs, G*vdim]. q [T, H, dim] -> out [T, H*vdim]. fp32 scores and accumulation. */
+int b200_attn_generic(void* out, const void* q, int64_t q_stride, const void* k, int64_t k_stride,
+                      const void* v, int64_t v_stride, const int32_t* block_tables, int32_t bt_stride,
+                      int32_t block_size, const int32_t* cu_q, const int32_t* cu_k, const int32_t* ctx_lens,
+                      int32_t num_seqs, int32_t max_q, int32_t num_heads, int32_t num_kv_heads, int32_t dim,
+                      int32_t vdim, float scale, int32_t dtype, b200_stream_t stream);
+
+/* Per head S_t = a_t S_(t-1) + k_t (b_t v_t)^T, o_t = S_t^T q_t; S fp32 [kdim, vdim] in state
+ * [slots, H, kdim, vdim]. q, k [T, groups*kdim] (head h reads group h / (H / groups)), v [T, H*vdim];
+ * out fp32 [T, H*vdim]. mode 0: a_t = decay[h], b_t = 1, optional silu on q, k, v as read. mode 1:
+ * step = softplus(dt[t, h] + dt_bias[h]), a_t = exp(-exp(a_log[h]) step), b_t = step, o_t += d_skip[h] v_t. */
+int b200_linear_recurrence(float* out, const void* q, int64_t q_stride, const void* k, int64_t k_stride,
+                           const void* v, int64_t v_stride, float* state, const int32_t* state_slots,
+                           const int32_t* cu_q, const int32_t* cu_k, const int32_t* ctx_lens,
+                           int32_t num_seqs, int32_t num_heads, int32_t groups, int32_t kdim, int32_t vdim,
+                           int32_t mode, int32_t act_silu, const float* decay, const void* dt,
+                           int64_t dt_stride, const float* dt_bias, const float* a_log, const float* d_skip,
+                           int32_t dtype, b200_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,333 @@
+// seq_ops.cu -- the row-wise kernels around the sequence mixers of the hybrid decoders:
+//
+//   residual_rmsnorm     h = norm(r)                      r: the fp32 residual stream
+//   residual_add_norms   r += norm_post(y); h = norm_pre(r)      one pass, both reductions in the CTA
+//   causal_conv          short depth-wise convolution over time with a per-sequence tail carried in a slot
+//   unitnorm_temp_cache  per-head unit RMS of q and k, position-dependent query temperature, K/V scatter
+//   gated_norm           (grouped) RMS norm and an output gate, in either order
+//   act_and_mul          act(gate) * up for the gated feed-forward
+//
+// All are bound by HBM traffic; arithmetic is fp32 whatever the element type. Shapes are free: no
+// multiple-of-8 rule, so that small and odd models run (a 16-byte path is taken where rows allow it).
+#include "seq_common.cuh"
+
+namespace b200 {
+
+// ------------------------------------------------------------------ norms over the fp32 residual
+// weight w is stored as the deviation from `offset`: y = x * rsqrt(mean x^2 + eps) * (offset + w)
+template <typename T>
+__global__ void __launch_bounds__(256)
+residual_rmsnorm_kernel(T* __restrict__ out, const float* __restrict__ res, const float* __restrict__ w,
+                        float offset, float eps, int hidden) {
+  __shared__ float red[32];
+  pdl_wait();
+  const float* r = res + (int64_t)blockIdx.x * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) ss += r[i] * r[i];
+  const float rstd = 1.0f / sqrtf(cta_sum(ss, red) / (float)hidden + eps);
+  T* o = out + (int64_t)blockIdx.x * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_f32<T>(r[i] * rstd * (offset + w[i]));
+}
+
+// r <- r + norm(y; w_post);  h <- norm(r; w_pre)  (h skipped when w_pre == nullptr). Dynamic smem: hidden floats.
+template <typename T>
+__global__ void __launch_bounds__(256)
+residual_add_norms_kernel(T* __restrict__ h, float* __restrict__ res, const T* __restrict__ y,
+                          const float* __restrict__ w_post, const float* __restrict__ w_pre, float offset,
+                          float eps, int hidden) {
+  extern __shared__ float row[];
+  __shared__ float red[32];
+  pdl_wait();
+  const T* yr = y + (int64_t)blockIdx.x * hidden;
+  float* r = res + (int64_t)blockIdx.x * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = to_f32<T>(yr[i]);
+    row[i] = v;
+    ss += v * v;
+  }
+  const float rstd = 1.0f / sqrtf(cta_sum(ss, red) / (float)hidden + eps);
+  float ss2 = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = r[i] + row[i] * rstd * (offset + w_post[i]);
+    r[i] = v;
+    row[i] = v;
+    ss2 += v * v;
+  }
+  if (w_pre == nullptr) return;
+  const float rstd2 = 1.0f / sqrtf(cta_sum(ss2, red) / (float)hidden + eps);
+  T* o = h + (int64_t)blockIdx.x * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+    o[i] = from_f32<T>(row[i] * rstd2 * (offset + w_pre[i]));
+}
+
+// ------------------------------------------------------------------ causal convolution over time
+// out[t, c] = act(bias[c] + sum_j w[c, j] * u[t - taps + 1 + j, c]), u = 0 before the sequence's start.
+// The last taps-1 inputs of every sequence live in state[slot] as [taps-1, C] (oldest first) between steps.
+// One thread = one channel x kConvSeg consecutive tokens of one sequence. Only the thread of a sequence's
+// first segment reads the carried tail, and the same thread writes the new one (from the chunk's last rows,
+// which it reads itself), so no other thread can see a half-updated tail.
+constexpr int kConvSeg = 16;
+constexpr int kConvMaxTaps = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+causal_conv_kernel(T* __restrict__ out, int64_t out_stride, const T* __restrict__ x, int64_t x_stride,
+                   const float* __restrict__ w, const float* __restrict__ bias, int act, T* __restrict__ state,
+                   const int* __restrict__ state_slots, const int* __restrict__ cu_q,
+                   const int* __restrict__ cu_k, const int* __restrict__ ctx_lens, int C, int taps) {
+  pdl_wait();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int s = blockIdx.z;
+  const SeqSpan sp = seq_span(cu_q, cu_k, ctx_lens, s);
+  const int t0 = blockIdx.y * kConvSeg;
+  if (c >= C || t0 >= sp.q_len) return;
+  const int hist = taps - 1;
+  const bool carried = state != nullptr && sp.first_pos() > 0;
+  T* tail = state != nullptr ? state + (int64_t)state_slots[s] * hist * C : nullptr;
+
+  float wt[kConvMaxTaps];
+#pragma unroll
+  for (int j = 0; j < kConvMaxTaps; ++j) wt[j] = j < taps ? w[(int64_t)c * taps + j] : 0.f;
+  const float b = bias != nullptr ? bias[c] : 0.f;
+
+  // input at token index i of this chunk (negative: the carried tail, or zeros at a sequence's start)
+  auto input = [&](int i) -> float {
+    if (i >= 0) return to_f32<T>(x[(int64_t)(sp.q_start + i) * x_stride + c]);
+    return carried ? to_f32<T>(tail[(int64_t)(hist + i) * C + c]) : 0.f;
+  };
+  float win[kConvMaxTaps];   // win[j] multiplies wt[j]; win[taps-1] is the current token
+#pragma unroll
+  for (int j = 0; j < kConvMaxTaps; ++j) win[j] = (j >= 1 && j < taps) ? input(t0 - taps + j) : 0.f;
+  // (win[1 .. taps-1] now hold inputs t0-taps+1 .. t0-1; the loop shifts before it loads)
+  const int t1 = min(t0 + kConvSeg, sp.q_len);
+  for (int t = t0; t < t1; ++t) {
+#pragma unroll
+    for (int j = 0; j < kConvMaxTaps - 1; ++j) win[j] = win[j + 1];
+    const float cur = input(t);
+#pragma unroll
+    for (int j = 0; j < kConvMaxTaps; ++j)
+      if (j == taps - 1) win[j] = cur;
+    float acc = b;
+#pragma unroll
+    for (int j = 0; j < kConvMaxTaps; ++j)
+      if (j < taps) acc += wt[j] * win[j];
+    if (act == 1) acc = silu_f(acc);
+    out[(int64_t)(sp.q_start + t) * out_stride + c] = from_f32<T>(acc);
+  }
+  if (t0 == 0 && tail != nullptr && hist > 0) {
+    float keep[kConvMaxTaps];
+#pragma unroll
+    for (int j = 0; j < kConvMaxTaps; ++j) keep[j] = j < hist ? input(sp.q_len - hist + j) : 0.f;
+#pragma unroll
+    for (int j = 0; j < kConvMaxTaps; ++j)
+      if (j < hist) tail[(int64_t)j * C + c] = from_f32<T>(keep[j]);
+  }
+}
+
+// ------------------------------------------------------------------ q/k unit norm, query temperature, K/V scatter
+// qkv: [T, H*dim | G*dim | G*vdim] (row stride given). Per head: q <- q / rms(q) * temp(pos), k <- k / rms(k),
+// temp(p) = 1 + coef * ln(floor((p + 1) / every) + 1). q and k are rewritten in place; k and v are also
+// stored at their cache slot when caches are bound. One warp per (token, head of q | k | v).
+template <typename T>
+__global__ void __launch_bounds__(256)
+unitnorm_temp_cache_kernel(T* __restrict__ qkv, int64_t stride, const int64_t* __restrict__ positions,
+                           float eps, float coef, int every, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                           const int* __restrict__ slots, int slot_pairs, int block_size, int num_tokens,
+                           int H, int G, int dim, int vdim) {
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int per_tok = H + 2 * G;
+  if (unit >= (int64_t)num_tokens * per_tok) return;
+  const int t = (int)(unit / per_tok), u = (int)(unit % per_tok);
+  int64_t slot = -1;
+  if (k_cache != nullptr && u >= H) {
+    slot = slot_pairs ? (int64_t)slots[2 * t] * block_size + slots[2 * t + 1] : (int64_t)slots[t];
+    if (slot < 0) return;
+  }
+  T* row = qkv + (int64_t)t * stride;
+  if (u >= H + G) {                                  // a value head: copy only
+    const int g = u - H - G;
+    if (k_cache == nullptr) return;
+    const T* src = row + (int64_t)H * dim + (int64_t)G * dim + (int64_t)g * vdim;
+    T* dst = v_cache + slot * ((int64_t)G * vdim) + (int64_t)g * vdim;
+    for (int i = lane; i < vdim; i += 32) dst[i] = src[i];
+    return;
+  }
+  T* x = row + (int64_t)u * dim;                     // q heads then k heads, both `dim` wide
+  float ss = 0.f;
+  for (int i = lane; i < dim; i += 32) {
+    const float v = to_f32<T>(x[i]);
+    ss += v * v;
+  }
+  float mul = 1.0f / sqrtf(warp_sum(ss) / (float)dim + eps);
+  if (u < H) {
+    const int64_t steps = (positions[t] + 1) / every;
+    mul *= 1.0f + coef * logf((float)steps + 1.0f);
+  }
+  T* dst = (u >= H && k_cache != nullptr) ? k_cache + slot * ((int64_t)G * dim) + (int64_t)(u - H) * dim : nullptr;
+  for (int i = lane; i < dim; i += 32) {
+    const T v = from_f32<T>(to_f32<T>(x[i]) * mul);
+    x[i] = v;
+    if (dst != nullptr) dst[i] = v;
+  }
+}
+
+// ------------------------------------------------------------------ gated (grouped) RMS norm
+// y: [rows, n] fp32 or T; gate: [rows, n] T with a row stride. One CTA per (row, group of n / groups):
+//   gate_first: out = norm_group(y * act(gate)) * w          (gate, then norm)
+//   else      : out = norm_group(y) * w * act(gate)          (norm, then gate)
+// w == nullptr: no norm at all, out = y * act(gate). gate_act: 0 sigmoid, 1 silu.
+template <typename T, typename Y>
+__global__ void __launch_bounds__(256)
+gated_norm_kernel(T* __restrict__ out, const Y* __restrict__ y, const T* __restrict__ gate,
+                  int64_t gate_stride, const float* __restrict__ w, float eps, int n, int groups,
+                  int gate_first, int gate_act) {
+  __shared__ float red[32];
+  pdl_wait();
+  const int64_t r = blockIdx.x;
+  const int len = n / groups, lo = blockIdx.y * len;
+  const Y* yr = y + r * n + lo;
+  const T* gr = gate + r * gate_stride + lo;
+  T* o = out + r * n + lo;
+  auto gate_at = [&](int i) -> float {
+    const float g = to_f32<T>(gr[i]);
+    return gate_act == 1 ? silu_f(g) : sigmoid_f(g);
+  };
+  if (w == nullptr) {
+    for (int i = threadIdx.x; i < len; i += blockDim.x) o[i] = from_f32<T>(to_f32<Y>(yr[i]) * gate_at(i));
+    return;
+  }
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < len; i += blockDim.x) {
+    float v = to_f32<Y>(yr[i]);
+    if (gate_first) v *= gate_at(i);
+    ss += v * v;
+  }
+  const float rstd = 1.0f / sqrtf(cta_sum(ss, red) / (float)len + eps);
+  for (int i = threadIdx.x; i < len; i += blockDim.x) {
+    float v = to_f32<Y>(yr[i]);
+    if (gate_first) v = v * gate_at(i) * rstd * w[lo + i];
+    else v = v * rstd * w[lo + i] * gate_at(i);
+    o[i] = from_f32<T>(v);
+  }
+}
+
+// ------------------------------------------------------------------ act(gate) * up
+// x: [rows, 2 * inter] (gate | up) -> out [rows, inter]. act: 0 silu, 1 relu, 2 gelu (tanh form).
+template <typename T>
+__global__ void __launch_bounds__(256)
+act_and_mul_kernel(T* __restrict__ out, const T* __restrict__ x, int64_t rows, int inter, int act) {
+  pdl_wait();
+  const int64_t total = rows * inter;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / inter;
+    const int c = (int)(i - r * inter);
+    const float g = to_f32<T>(x[r * 2 * inter + c]), u = to_f32<T>(x[r * 2 * inter + inter + c]);
+    const float a = act == 1 ? fmaxf(g, 0.f) : act == 2 ? gelu_tanh_f(g) : silu_f(g);
+    out[i] = from_f32<T>(a * u);
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_residual_rmsnorm(void* out, const float* residual, const float* weight, float offset,
+                                     float eps, int32_t rows, int32_t hidden, int32_t dtype,
+                                     b200_stream_t stream) {
+  B200_RETURN_IF(rows < 0 || hidden <= 0, B200_ERR_BAD_SHAPE);
+  if (rows == 0) return B200_OK;
+  B200_RETURN_IF(!out || !residual || !weight, B200_ERR_NULL_POINTER);
+  B200_DISPATCH_3(dtype, T, launch_pdl(residual_rmsnorm_kernel<T>, dim3(rows), dim3(256), 0,
+                                       (cudaStream_t)stream, (T*)out, residual, weight, offset, eps, hidden));
+  return finish_launch();
+}
+
+extern "C" int b200_residual_add_norms(void* h, float* residual, const void* y, const float* w_post,
+                                       const float* w_pre, float offset, float eps, int32_t rows,
+                                       int32_t hidden, int32_t dtype, b200_stream_t stream) {
+  B200_RETURN_IF(rows < 0 || hidden <= 0, B200_ERR_BAD_SHAPE);
+  if (rows == 0) return B200_OK;
+  B200_RETURN_IF(!residual || !y || !w_post || (w_pre && !h), B200_ERR_NULL_POINTER);
+  const size_t smem = (size_t)hidden * sizeof(float);
+  B200_RETURN_IF(smem > 200 * 1024, B200_ERR_UNSUPPORTED);
+  B200_DISPATCH_3(dtype, T, {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(residual_add_norms_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_pdl(residual_add_norms_kernel<T>, dim3(rows), dim3(256), smem, (cudaStream_t)stream, (T*)h,
+               residual, (const T*)y, w_post, w_pre, offset, eps, hidden);
+  });
+  return finish_launch();
+}
+
+extern "C" int b200_causal_conv(void* out, int64_t out_stride, const void* x, int64_t x_stride,
+                                const float* weight, const float* bias, int32_t act, void* state,
+                                const int32_t* state_slots, const int32_t* cu_q, const int32_t* cu_k,
+                                const int32_t* ctx_lens, int32_t num_seqs, int32_t max_q, int32_t channels,
+                                int32_t taps, int32_t dtype, b200_stream_t stream) {
+  B200_RETURN_IF(num_seqs < 0 || max_q < 0 || channels <= 0 || taps <= 0, B200_ERR_BAD_SHAPE);
+  B200_RETURN_IF(taps > kConvMaxTaps || taps - 1 > kConvSeg, B200_ERR_UNSUPPORTED);
+  if (num_seqs == 0 || max_q == 0) return B200_OK;
+  B200_RETURN_IF(!out || !x || !weight || (cu_q == nullptr) == (ctx_lens == nullptr) || (cu_q && !cu_k) ||
+                     (state && !state_slots), B200_ERR_NULL_POINTER);
+  B200_RETURN_IF(out == x, B200_ERR_UNSUPPORTED);
+  const dim3 grid((channels + 127) / 128, (max_q + kConvSeg - 1) / kConvSeg, num_seqs);
+  B200_DISPATCH_3(dtype, T, launch_pdl(causal_conv_kernel<T>, grid, dim3(128), 0, (cudaStream_t)stream, (T*)out,
+                                       out_stride, (const T*)x, x_stride, weight, bias, act, (T*)state,
+                                       state_slots, cu_q, cu_k, ctx_lens, channels, taps));
+  return finish_launch();
+}
+
+extern "C" int b200_unitnorm_temp_cache(void* qkv, int64_t stride, const int64_t* positions, float eps,
+                                        float coef, int32_t every, void* k_cache, void* v_cache,
+                                        const int32_t* slots, int32_t slot_pairs, int32_t block_size,
+                                        int32_t num_tokens, int32_t num_heads, int32_t num_kv_heads,
+                                        int32_t dim, int32_t vdim, int32_t dtype, b200_stream_t stream) {
+  B200_RETURN_IF(num_tokens < 0 || num_heads <= 0 || num_kv_heads <= 0 || dim <= 0 || vdim <= 0 || every <= 0,
+                 B200_ERR_BAD_SHAPE);
+  if (num_tokens == 0) return B200_OK;
+  B200_RETURN_IF(!qkv || !positions || (k_cache == nullptr) != (v_cache == nullptr) || (k_cache && !slots),
+                 B200_ERR_NULL_POINTER);
+  const int64_t units = (int64_t)num_tokens * (num_heads + 2 * num_kv_heads);
+  const dim3 grid((unsigned)((units + 7) / 8));
+  B200_DISPATCH_3(dtype, T, launch_pdl(unitnorm_temp_cache_kernel<T>, grid, dim3(256), 0, (cudaStream_t)stream,
+                                       (T*)qkv, stride, positions, eps, coef, every, (T*)k_cache, (T*)v_cache,
+                                       slots, slot_pairs, block_size, num_tokens, num_heads, num_kv_heads, dim,
+                                       vdim));
+  return finish_launch();
+}
+
+extern "C" int b200_gated_norm(void* out, const void* y, int32_t y_is_f32, const void* gate,
+                               int64_t gate_stride, const float* weight, float eps, int32_t rows, int32_t n,
+                               int32_t groups, int32_t gate_first, int32_t gate_act, int32_t dtype,
+                               b200_stream_t stream) {
+  B200_RETURN_IF(rows < 0 || n <= 0 || groups <= 0 || n % groups != 0, B200_ERR_BAD_SHAPE);
+  if (rows == 0) return B200_OK;
+  B200_RETURN_IF(!out || !y || !gate, B200_ERR_NULL_POINTER);
+  const dim3 grid(rows, weight ? groups : 1);
+  const int g = weight ? groups : 1;
+  B200_DISPATCH_3(dtype, T, {
+    if (y_is_f32)
+      launch_pdl(gated_norm_kernel<T, float>, grid, dim3(256), 0, (cudaStream_t)stream, (T*)out,
+                 (const float*)y, (const T*)gate, gate_stride, weight, eps, n, g, gate_first, gate_act);
+    else
+      launch_pdl(gated_norm_kernel<T, T>, grid, dim3(256), 0, (cudaStream_t)stream, (T*)out, (const T*)y,
+                 (const T*)gate, gate_stride, weight, eps, n, g, gate_first, gate_act);
+  });
+  return finish_launch();
+}
+
+extern "C" int b200_act_and_mul(void* out, const void* x, int32_t rows, int32_t inter, int32_t act,
+                                int32_t dtype, b200_stream_t stream) {
+  B200_RETURN_IF(rows < 0 || inter <= 0 || act < 0 || act > 2, B200_ERR_BAD_SHAPE);
+  if (rows == 0) return B200_OK;
+  B200_RETURN_IF(!out || !x, B200_ERR_NULL_POINTER);
+  const int64_t total = (int64_t)rows * inter;
+  int grid = (int)((total + 255) / 256);
+  if (grid > 148 * 16) grid = 148 * 16;
+  B200_DISPATCH_3(dtype, T, launch_pdl(act_and_mul_kernel<T>, dim3(grid), dim3(256), 0, (cudaStream_t)stream,
+                                       (T*)out, (const T*)x, (int64_t)rows, inter, act));
+  return finish_launch();
+}

@@ -15,7 +15,7 @@ _LIB_ENV = "B200ATTN_LIB"
 _HERE = os.path.dirname(os.path.abspath(__file__))
 DEFAULT_LIB_PATH = os.path.normpath(os.path.join(_HERE, "..", "lib", "libb200attn.so"))
 
-BF16, F16 = 0, 1
+BF16, F16, F32 = 0, 1, 2
 
 # name -> (restype, argtypes); the single source of truth for the exported symbol list.
 PROTOTYPES = {
@@ -98,6 +98,27 @@ PROTOTYPES = {
     "b200_comm_get_handle": (c_int32, [c_void_p, c_void_p]),
     "b200_comm_open_handle": (c_int32, [c_void_p, c_void_p]),
     "b200_comm_close_handle": (c_int32, [c_void_p]),
+    # sequence-mixer kernels of the hybrid decoders (seq_ops.cu, seq_mixers.cu); bf16 / fp16 / fp32
+    "b200_residual_rmsnorm": (c_int32, [c_void_p, c_void_p, c_void_p, c_float, c_float, c_int32, c_int32,
+                                        c_int32, c_void_p]),
+    "b200_residual_add_norms": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float,
+                                          c_int32, c_int32, c_int32, c_void_p]),
+    "b200_causal_conv": (c_int32, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int32, c_void_p,
+                                   c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
+                                   c_int32, c_void_p]),
+    "b200_unitnorm_temp_cache": (c_int32, [c_void_p, c_int64, c_void_p, c_float, c_float, c_int32, c_void_p,
+                                           c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_int32,
+                                           c_int32, c_int32, c_int32, c_void_p]),
+    "b200_gated_norm": (c_int32, [c_void_p, c_void_p, c_int32, c_void_p, c_int64, c_void_p, c_float, c_int32,
+                                  c_int32, c_int32, c_int32, c_int32, c_int32, c_void_p]),
+    "b200_act_and_mul": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p]),
+    "b200_attn_generic": (c_int32, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p,
+                                    c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,
+                                    c_int32, c_int32, c_int32, c_float, c_int32, c_void_p]),
+    "b200_linear_recurrence": (c_int32, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
+                                         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32,
+                                         c_int32, c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p,
+                                         c_int64, c_void_p, c_void_p, c_void_p, c_int32, c_void_p]),
     "b200_sample": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int64, c_uint64,
                               c_uint64, c_void_p, c_int32, c_void_p]),
 }

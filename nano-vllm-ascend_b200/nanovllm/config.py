@@ -18,10 +18,61 @@ class GraphMode(Enum):
     REDUCE_OVERHEAD = "reduce-overhead"
 
 
+class NativeConfig:
+    """Configuration of an architecture that is described by its own ``config.json`` rather than by a
+    transformers config class: a JSON object with an ``"architecture"`` string and whatever the model class
+    reads (``to_dict()``). It offers the few attributes the engine asks of any config."""
+
+    def __init__(self, data: dict):
+        self._data = dict(data)
+        self.architectures = [data["architecture"]]
+        self.dtype = data.get("dtype", "bfloat16")
+        self.eos_token_id = data.get("eos_token_id", -1)
+        self.max_position_embeddings = data.get("max_position_embeddings")
+
+    def to_dict(self) -> dict:
+        return dict(self._data)
+
+    @staticmethod
+    def read(folder: str):
+        """The folder's config.json as a NativeConfig, or None when it is a transformers config."""
+        import json
+        path = os.path.join(folder, "config.json")
+        if not os.path.isfile(path):
+            return None
+        with open(path) as f:
+            data = json.load(f)
+        return NativeConfig(data) if isinstance(data.get("architecture"), str) else None
+
+
+def zegopel_preset(width: int, pattern: str, repeats: int, vocab: int = 32768, head_dim: int = 128) -> dict:
+    """A Zegopel configuration of realistic layer sizes for synthetic benchmarks: `pattern` is a string over
+    a (attention + feed-forward), l (lightning) and m (mamba2), repeated `repeats` times."""
+    H = width // head_dim
+    kv = max(1, H // 4)
+    decay = [1.0 - 2.0 ** (-3 - 5 * i / max(1, H - 1)) for i in range(H)]
+    entry = {
+        "a": {"type": "attention", "mlp": {"kind": "dense", "ff": 3 * width},
+              "mixer": {"heads": H, "kv_heads": kv, "dim": head_dim, "vdim": head_dim, "conv": 3,
+                        "scale": head_dim ** -0.5 * 8.0, "q_temp": {"coef": 0.1, "every": 1024}}},
+        "l": {"type": "lightning", "mlp": None,
+              "mixer": {"heads": H, "dim": head_dim, "vdim": head_dim, "decay": decay}},
+        "m": {"type": "mamba2", "mlp": None,
+              "mixer": {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 8 if H >= 8 else 1,
+                        "norm_groups": 8 if H >= 8 else 1, "conv": 4}},
+    }
+    return {"architecture": "Zegopel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "layers": [entry[ch] for ch in pattern] * repeats}
+
+
 def preset_hf_config(name: str):
     """Architecture presets built offline from the public model cards."""
     from transformers import LlamaConfig, Qwen3Config, Qwen3MoeConfig
     key = name.lower().rstrip("/").split("/")[-1]
+    if key == "zegopel-1k":          # 28 layers at width 1024: the size class of qwen3-0.6b
+        return NativeConfig(zegopel_preset(1024, "almlalm", 4, vocab=151936))
+    if key == "tiny-zegopel":
+        return NativeConfig(zegopel_preset(128, "alm", 1, vocab=512, head_dim=32))
     if key == "qwen3-0.6b":
         c = Qwen3Config(vocab_size=151936, hidden_size=1024, num_hidden_layers=28,
                         num_attention_heads=16, num_key_value_heads=8, head_dim=128,
@@ -106,6 +157,13 @@ class Config:
     tp_shard_emulation: int = 0        # profiling aid: N > 1 builds rank 0's shard of an N-way tensor-parallel
                                        # model in ONE process, collectives skipped (per-rank kernel timeline of a
                                        # TP=N step on one GPU; outputs are meaningless). tensor_parallel_size stays 1
+    dtype: str = "auto"                # "auto": the checkpoint's 16-bit type; "bfloat16" / "float16"; "float32" for
+                                       # models whose kernels all have a true 32-bit form (no TF32 anywhere)
+    num_state_slots: int = -1          # per-sequence state rows (recurrent state, convolution tails) of hybrid
+                                       # models: set by the runner (max_num_seqs) when the model needs them, else 0
+    enable_prefix_caching: bool = True # the runner turns it off for models whose state cannot be rebuilt from
+                                       # cached K/V blocks
+    return_logits: bool = False        # keep every step's logits at the requested rows (scoring / trace replay)
     kv_cache_dtype: str = "auto"       # "auto": the model dtype (reference behaviour); "fp8" /
                                        # "fp8_e4m3": e4m3 bytes, per-tensor scale 1.0
     # Two-micro-batch decode (engine/model_runner.py::_forward_overlapped): a decode step whose attention
@@ -128,8 +186,12 @@ class Config:
         assert self.kvcache_block_size % 16 == 0
         assert 1 <= self.tensor_parallel_size <= 8
         assert self.kv_cache_dtype in ("auto", "fp8", "fp8_e4m3"), self.kv_cache_dtype
+        assert self.dtype in ("auto", "bfloat16", "float16", "float32"), self.dtype
         if self.hf_config is None:
-            if os.path.isdir(self.model):
+            native = NativeConfig.read(self.model) if os.path.isdir(self.model) else None
+            if native is not None:
+                self.hf_config = native
+            elif os.path.isdir(self.model):
                 from transformers import AutoConfig
                 self.hf_config = AutoConfig.from_pretrained(self.model,
                                                             trust_remote_code=self.trust_remote_code)

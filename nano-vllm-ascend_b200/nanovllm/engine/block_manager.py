@@ -39,7 +39,14 @@ class Block:
 
 class BlockManager:
 
-    def __init__(self, num_blocks: int, block_size: int, non_cache_token_ids=None):
+    def __init__(self, num_blocks: int, block_size: int, non_cache_token_ids=None, num_state_slots: int = 0,
+                 prefix_caching: bool = True):
+        """num_state_slots > 0: every admitted sequence also takes one row of the per-sequence state pool
+        (hybrid models) and gives it back with its blocks. prefix_caching=False: no block is ever shared or
+        found by hash (models whose state at a prefix's end cannot be rebuilt from cached K/V)."""
+        self.num_state_slots = num_state_slots
+        self.free_state_slots: deque[int] = deque(range(num_state_slots))
+        self.prefix_caching = prefix_caching
         self.block_size = block_size
         self.blocks = [Block(i) for i in range(num_blocks)]
         self.hash_to_block_id: dict[int, int] = {}
@@ -81,6 +88,8 @@ class BlockManager:
 
     # ------------------------------------------------------------------ prompt admission
     def can_allocate(self, seq: Sequence) -> bool:
+        if self.num_state_slots and not self.free_state_slots:
+            return False
         return len(self.free_block_ids) >= seq.num_blocks
 
     def allocate(self, seq: Sequence) -> None:
@@ -89,6 +98,12 @@ class BlockManager:
         # counter (block_manager.py:62-88) and ignores it in its runner; here prepare_prefill and the
         # chunked scheduler consume it, so a stale value would skip tokens whose K/V are gone
         seq.num_cached_tokens = 0
+        if self.num_state_slots:
+            seq.state_slot = self.free_state_slots.popleft()
+        if not self.prefix_caching:
+            for _ in range(seq.num_blocks):
+                seq.block_table.append(self._take(self.free_block_ids[0]).block_id)
+            return
         hashes = self._chain(seq)
         # length of the cached prefix: leading blocks whose hash is known AND whose stored
         # tokens really are these tokens (hash collisions do not count as hits)
@@ -138,6 +153,18 @@ class BlockManager:
             if block.ref_count == 0:
                 self._give_back(block_id)
         seq.block_table.clear()
+        if seq.state_slot >= 0:
+            self.free_state_slots.append(seq.state_slot)
+            seq.state_slot = -1
+
+    def can_extend(self, seq: Sequence) -> bool:
+        return len(self.free_block_ids) >= seq.num_blocks - len(seq.block_table)
+
+    def extend(self, seq: Sequence) -> None:
+        """Blocks for tokens that were added to an admitted sequence several at a time (given tokens fed
+        step by step); such blocks are never registered for prefix hits."""
+        while len(seq.block_table) < seq.num_blocks:
+            seq.block_table.append(self._take(self.free_block_ids[0]).block_id)
 
     # ------------------------------------------------------------------ decode growth
     def can_append(self, seq: Sequence) -> bool:
@@ -148,6 +175,10 @@ class BlockManager:
         table = seq.block_table
         last = self.blocks[table[-1]]
         fill = len(seq) % self.block_size
+        if not self.prefix_caching:
+            if fill == 1 or self.block_size == 1:
+                table.append(self._take(self.free_block_ids[0]).block_id)
+            return
         if fill == 1:                       # the newest token opened a block
             assert last.hash != NO_HASH
             fresh = self.free_block_ids[0]

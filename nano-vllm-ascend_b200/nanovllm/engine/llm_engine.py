@@ -113,6 +113,26 @@ class LLMEngine:
                    for s in seqs if s.is_finished]
         return outputs, num_tokens
 
+    def step_given(self, entries: list[tuple[str, list[int], list[int]]], end: list[str] = ()):
+        """One engine step over GIVEN tokens (scoring, replay of a recorded schedule): every entry is
+        (request id, the request's next tokens, the places among these tokens whose logits are wanted).
+        All entries run as one batch through the scheduler's block manager and the runner's step, prompt
+        portions beside single tokens; a request is admitted at its first entry and gives back its blocks
+        and state slot when it is named in ``end``. Nothing is sampled. Returns fp32 logits
+        [wanted places in entry order, vocab] on the host, or None. Needs ``return_logits=True``."""
+        seqs, is_prefill = self.scheduler.schedule_given([(rid, tokens) for rid, tokens, _ in entries])
+        rows, base = [], 0
+        for i, (_, tokens, want) in enumerate(entries):
+            if any(w < 0 or w >= len(tokens) for w in want):
+                raise ValueError("a wanted place lies outside the entry's tokens")
+            rows += [base + w for w in want] if is_prefill else [i] * len(want)
+            base += len(tokens)
+        logits = self.model_runner.call("run", seqs, is_prefill, rows)
+        self.scheduler.postprocess_given(seqs)
+        for request_id in end:
+            self.scheduler.finish_given(request_id)
+        return logits
+
     def generate(self, prompts, sampling_params, use_tqdm: bool = True) -> list[dict]:
         pbar = None
         if use_tqdm:

@@ -34,7 +34,14 @@ from .sequence import Sequence
 _SHM_PREFIX = "nano_vllm_b200"
 
 
-def _resolve_dtype(hf_config) -> torch.dtype:
+def _resolve_dtype(hf_config, asked: str = "auto", model_cls=None) -> torch.dtype:
+    if asked == "float32":
+        if not getattr(model_cls, "supports_fp32", False):
+            raise ValueError("float32 serving needs a model whose kernels all have a 32-bit form "
+                             f"({getattr(model_cls, '__name__', model_cls)} has 16-bit kernels only)")
+        return torch.float32
+    if asked in ("bfloat16", "float16"):
+        return getattr(torch, asked)
     dt = getattr(hf_config, "torch_dtype", None) or getattr(hf_config, "dtype", None)
     if isinstance(dt, str):
         dt = {"bf16": torch.bfloat16, "bfloat16": torch.bfloat16, "fp16": torch.float16,
@@ -75,11 +82,15 @@ class ModelRunner:
         self.device = torch.device("cuda", local if self.world_size > 1 or self.spmd else
                                    torch.cuda.current_device())
         torch.cuda.set_device(self.device)
-        self.dtype = _resolve_dtype(self.hf_config)
-
         arch = self.hf_config.architectures[0]
         if arch not in model_dict:
             raise ValueError(f"architecture {arch} is outside the hot-path scope (dense Qwen3/Qwen2/Llama)")
+        self.dtype = _resolve_dtype(self.hf_config, config.dtype, model_dict[arch])
+        if self.dtype == torch.float32:
+            # true 32-bit products in the library GEMMs: no TF32, no reduced-precision accumulation
+            torch.backends.cuda.matmul.allow_tf32 = False
+            torch.backends.cudnn.allow_tf32 = False
+            torch.set_float32_matmul_precision("highest")
         prev = torch.get_default_dtype()
         torch.set_default_dtype(self.dtype)
         try:
@@ -94,12 +105,20 @@ class ModelRunner:
         else:
             n_params = sum(p.numel() for p in self.model.parameters())
             on_device = config.init_device == "cuda" or (config.init_device == "auto" and n_params > 2e9)
-            if on_device:
+            if hasattr(self.model, "random_init"):
+                self.model.random_init(config.seed)
+            elif on_device:
                 device_init(self.model, seed=config.seed, std=config.init_std)
             else:
                 seeded_init(self.model, seed=config.seed, norm_jitter=config.norm_jitter, std=config.init_std)
         self.model.eval()
         self.spec = self.model.spec
+        # hybrid models: modules that keep per-sequence state (recurrent state, convolution tails) declare it
+        # with state_shapes(); one pool row per state slot, slots handed out by the scheduler's block manager
+        self.state_modules = [m for m in self.model.modules() if hasattr(m, "state_shapes") and m.state_shapes()]
+        config.num_state_slots = config.max_num_seqs if self.state_modules else 0
+        config.enable_prefix_caching = bool(getattr(self.model, "prefix_caching", True)) and not self.state_modules
+        self.d_logits = None                       # Config.return_logits: [max_num_seqs, vocab] fp32, set below
         self.comm = None
         if self.world_size > 1:
             from ..comm import PeerAllReduce, set_comm
@@ -119,10 +138,10 @@ class ModelRunner:
         self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
         self.split_graphs: dict[int, torch.cuda.CUDAGraph] = {}      # two-micro-batch form of the large buckets
         # bytes one layer's attention reads per cached token, and one layer's weights (split criterion)
-        self._kv_token_bytes = 2 * max(1, self.spec.num_kv_heads // self.shard_world) * self.spec.head_dim * \
-            self.kv_cache.dtype.itemsize
-        self._layer_weight_bytes = sum(p.numel() * p.element_size()
-                                       for p in self.model.model.layers[0].parameters())
+        self._kv_token_bytes = 2 * max(1, getattr(self.spec, "num_kv_heads", 1) // self.shard_world) * \
+            getattr(self.spec, "head_dim", 1) * self.kv_cache.dtype.itemsize
+        self._layer_weight_bytes = sum(p.numel() * p.element_size() for p in
+                                       getattr(self.model, "model", self.model).layers[0].parameters())
         self._num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
         if not self.enforce_eager:
             self._capture_decode_graphs()
@@ -214,19 +233,25 @@ class ModelRunner:
         torch.cuda.synchronize()
         torch.cuda.empty_cache()
 
+    def _available_cache_bytes(self) -> int:
+        cfg = self.config
+        free, total = torch.cuda.mem_get_info()
+        stats = torch.cuda.memory_stats()
+        used = total - free
+        peak, current = stats["allocated_bytes.all.peak"], stats["allocated_bytes.all.current"]
+        return int(total * cfg.gpu_memory_utilization - used - peak + current)
+
     def _allocate_kv_cache(self):
         cfg, spec = self.config, self.spec
+        attn_modules = [m for m in self.model.modules() if hasattr(m, "k_cache") and hasattr(m, "v_cache")]
+        if self.state_modules or any(hasattr(m, "cache_rows") for m in attn_modules):
+            return self._allocate_hybrid_cache(attn_modules)
         kv_heads = max(1, spec.num_kv_heads // self.shard_world)    # < 1: kv heads replicated (linear.py)
         # e4m3 caches are kept as raw bytes (uint8); the attention layers dispatch on that dtype
         cache_dtype = self.dtype if cfg.kv_cache_dtype == "auto" else torch.uint8
         block_bytes = 2 * spec.num_layers * self.block_size * kv_heads * spec.head_dim * cache_dtype.itemsize
         if cfg.num_kvcache_blocks <= 0:
-            free, total = torch.cuda.mem_get_info()
-            stats = torch.cuda.memory_stats()
-            used = total - free
-            peak, current = stats["allocated_bytes.all.peak"], stats["allocated_bytes.all.current"]
-            available = total * cfg.gpu_memory_utilization - used - peak + current
-            cfg.num_kvcache_blocks = int(available) // block_bytes
+            cfg.num_kvcache_blocks = self._available_cache_bytes() // block_bytes
         if self.world_size > 1:
             # every rank must hold every block id the (rank-0) scheduler can hand out
             n = torch.tensor([cfg.num_kvcache_blocks], dtype=torch.int64, device=self.device)
@@ -236,12 +261,49 @@ class ModelRunner:
         self.kv_cache = torch.zeros(2, spec.num_layers, cfg.num_kvcache_blocks, self.block_size,
                                     kv_heads * spec.head_dim, dtype=cache_dtype, device=self.device)
         layer = 0
-        for module in self.model.modules():
-            if hasattr(module, "k_cache") and hasattr(module, "v_cache"):
-                module.k_cache = self.kv_cache[0, layer]
-                module.v_cache = self.kv_cache[1, layer]
-                module.layer_id = layer
-                layer += 1
+        for module in attn_modules:
+            module.k_cache = self.kv_cache[0, layer]
+            module.v_cache = self.kv_cache[1, layer]
+            module.layer_id = layer
+            layer += 1
+
+    def _allocate_hybrid_cache(self, attn_modules):
+        """Caches of a model whose layers differ: only its attention layers hold K/V, with their own row
+        widths (key and value sizes may differ), and every stateful module gets a pool of
+        max_num_seqs + 1 rows (the last one is the dummy row of padded graph rows) for what it carries from
+        token to token. The state pool is taken off the memory budget first; blocks fill the rest."""
+        cfg = self.config
+        if cfg.kv_cache_dtype != "auto":
+            raise ValueError("fp8 KV caches are not available for hybrid models")
+        if self.world_size > 1:
+            raise ValueError("hybrid models run on one GPU per replica")
+        item = self.dtype.itemsize
+        rows = [m.cache_rows() for m in attn_modules]
+        slots = cfg.max_num_seqs + 1
+        self.state_pools = []
+        state_bytes = 0
+        for m in self.state_modules:
+            for attr, (shape, dt) in m.state_shapes().items():
+                pool = torch.zeros(slots, *shape, dtype=dt or self.dtype, device=self.device)
+                setattr(m, attr, pool)
+                self.state_pools.append(pool)
+                state_bytes += pool.numel() * pool.element_size()
+        block_bytes = sum(k + v for k, v in rows) * self.block_size * item
+        if cfg.num_kvcache_blocks <= 0:
+            if block_bytes:
+                cfg.num_kvcache_blocks = self._available_cache_bytes() // block_bytes
+            else:                                    # no attention layer: block ids only count tokens
+                cfg.num_kvcache_blocks = cfg.max_num_seqs * (-(-cfg.max_model_len // self.block_size)) + 1
+        assert cfg.num_kvcache_blocks > 1, "not enough memory for the KV cache"
+        nb, bs = cfg.num_kvcache_blocks, self.block_size
+        self.kv_cache = torch.zeros(nb * bs * sum(k + v for k, v in rows), dtype=self.dtype, device=self.device)
+        off = 0
+        for layer, (m, (k_row, v_row)) in enumerate(zip(attn_modules, rows)):
+            m.k_cache = self.kv_cache[off:off + nb * bs * k_row].view(nb, bs, k_row)
+            off += nb * bs * k_row
+            m.v_cache = self.kv_cache[off:off + nb * bs * v_row].view(nb, bs, v_row)
+            off += nb * bs * v_row
+            m.layer_id = layer
 
     # ------------------------------------------------------------------ prefill metadata
     def prepare_prefill(self, seqs: list[Sequence]):
@@ -281,11 +343,13 @@ class ModelRunner:
         def as_dev(data, dt):
             host = torch.from_numpy(data) if isinstance(data, np.ndarray) else torch.tensor(data, dtype=dt)
             return host.to(dt).pin_memory().to(dev, non_blocking=True)
+        state_slots = as_dev([max(s.state_slot, 0) for s in seqs], torch.int32) \
+            if self.state_modules and all(s.state_slot >= 0 for s in seqs) else None
         set_context(True, cu_seqlens_q=as_dev(cu_q, torch.int32), cu_seqlens_k=as_dev(cu_k, torch.int32),
                     max_seqlen_q=max_q, max_seqlen_k=max_k,
                     slot_mapping=as_dev(slots, torch.int32) if slots is not None else None,
                     context_lens=None, block_tables=block_tables, is_enforce_eager=True,
-                    real_bs=len(seqs), block_size=bs, paged_prefill=hit)
+                    real_bs=len(seqs), block_size=bs, paged_prefill=hit, state_slots=state_slots)
         return as_dev(ids, torch.int64), as_dev(pos, torch.int64)
 
     def _dense_block_tables(self, seqs):
@@ -296,11 +360,12 @@ class ModelRunner:
     # ------------------------------------------------------------------ decode metadata
     def _init_decode_buffers(self):
         """One pinned host buffer + one device buffer holding every decode input:
-        [ids i64 | positions i64 | slots i32x2 | context_lens i32 | temperatures f32 | block_tables i32]."""
+        [ids i64 | positions i64 | slots i32x2 | context_lens i32 | temperatures f32 | state slots i32 |
+        block_tables i32]."""
         cfg = self.config
         B = cfg.max_num_seqs
         self.max_blocks = (cfg.max_model_len + self.block_size - 1) // self.block_size
-        sizes = [B * 8, B * 8, B * 8, B * 4, B * 4, B * self.max_blocks * 4]
+        sizes = [B * 8, B * 8, B * 8, B * 4, B * 4, B * 4, B * self.max_blocks * 4]
         offs = np.concatenate([[0], np.cumsum([(s + 255) // 256 * 256 for s in sizes])])
         self._stage_host = torch.zeros(int(offs[-1]), dtype=torch.uint8, pin_memory=True)
         self._stage_dev = torch.zeros(int(offs[-1]), dtype=torch.uint8, device=self.device)
@@ -308,14 +373,18 @@ class ModelRunner:
         def views(buf):
             seg = lambda i, dt, shape: buf[int(offs[i]):int(offs[i]) + sizes[i]].view(dt).view(shape)
             return (seg(0, torch.int64, (B,)), seg(1, torch.int64, (B,)), seg(2, torch.int32, (B, 2)),
-                    seg(3, torch.int32, (B,)), seg(4, torch.float32, (B,)),
-                    seg(5, torch.int32, (B, self.max_blocks)))
-        self.d_ids, self.d_pos, self.d_slots, self.d_ctx, self.d_temp, self.d_tables = views(self._stage_dev)
+                    seg(3, torch.int32, (B,)), seg(4, torch.float32, (B,)), seg(5, torch.int32, (B,)),
+                    seg(6, torch.int32, (B, self.max_blocks)))
+        (self.d_ids, self.d_pos, self.d_slots, self.d_ctx, self.d_temp, self.d_state,
+         self.d_tables) = views(self._stage_dev)
         h = views(self._stage_host)
-        self.h_ids, self.h_pos, self.h_slots, self.h_ctx, self.h_temp, self.h_tables = [t.numpy() for t in h]
+        (self.h_ids, self.h_pos, self.h_slots, self.h_ctx, self.h_temp, self.h_state,
+         self.h_tables) = [t.numpy() for t in h]
         self.h_tables.fill(-1)
         self._stage_dev.copy_(self._stage_host)
-        self._head_bytes = int(offs[5])          # everything before the block tables
+        self._head_bytes = int(offs[6])          # everything before the block tables
+        if self.config.return_logits:
+            self.d_logits = torch.zeros(B, self.spec.vocab_size, dtype=torch.float32, device=self.device)
         self._row_owner = [-1] * B               # seq_id whose table sits in row i
         self._row_len = [0] * B                  # how many entries of that table are staged
         self.d_out = torch.zeros(B, dtype=torch.int64, device=self.device)
@@ -341,6 +410,9 @@ class ModelRunner:
         self.h_slots[:n, 0] = [s.block_table[-1] for s in seqs]
         self.h_slots[:n, 1] = (lens - 1) % bs
         self.h_temp[:n] = [0.0 if s.greedy else s.temperature for s in seqs]
+        if self.state_modules:
+            self.h_state[:n] = [s.state_slot for s in seqs]
+            self.h_state[n:padded] = self.config.max_num_seqs          # the dummy row of the state pools
         if padded > n:
             self.h_ids[n:padded] = 0
             self.h_pos[n:padded] = 0
@@ -388,13 +460,16 @@ class ModelRunner:
         set_context(False, slot_mapping=self.d_slots[lo:bs], context_lens=self.d_ctx[lo:bs],
                     block_tables=self.d_tables[lo:bs], is_enforce_eager=self.enforce_eager,
                     real_bs=real_bs, block_size=self.block_size,
-                    decode_attn_ctas=self._attn_ctas(bs) if ctas is None else ctas, own_gemm=own_gemm)
+                    decode_attn_ctas=self._attn_ctas(bs) if ctas is None else ctas, own_gemm=own_gemm,
+                    state_slots=self.d_state[lo:bs] if self.state_modules else None)
 
     # ------------------------------------------------------------------ the decode step
     def _overlap_split(self, bs: int) -> int:
         """Rows of the first micro-batch if a `bs`-row decode step MAY run as two micro-batches, else 0:
         single GPU (the chain has no collective), dense MLPs (a split would stream every expert twice)."""
         least = self.config.decode_overlap_min_batch
+        if not getattr(getattr(self, "model", None), "split_decode", True):
+            return 0
         if least <= 0 or bs < max(least, 16) or self.shard_world > 1 or self.spec.num_experts > 0:
             return 0
         if self.kv_cache.dtype == torch.uint8:
@@ -458,6 +533,10 @@ class ModelRunner:
             self._sample_sharded(hidden, self.d_temp[:bs], self.d_keys[:bs], self.d_out[:bs])
             return
         logits = self.model.compute_logits(hidden)
+        if self.d_logits is not None:
+            self.d_logits[:bs].copy_(logits)
+        if logits.dtype == torch.float32:
+            logits = logits.to(torch.bfloat16)         # the sampling kernel reads 16-bit logits
         self.d_rng.add_(1)
         if self.rank == 0:
             self.sampler(logits, self.d_temp[:bs], out=self.d_out[:bs], step_offset=self.d_rng)
@@ -496,12 +575,33 @@ class ModelRunner:
                 (self.split_graphs if two_halves else self.graphs)[bs] = graph
         reset_context()
         torch.cuda.synchronize()
-        self.kv_cache[:, :, -1].zero_()                # the dummy block soaked up warm-up writes
+        self._zero_dummy_block()                       # the dummy block soaked up warm-up writes
+
+    def _zero_dummy_block(self):
+        if self.kv_cache.dim() == 5:
+            self.kv_cache[:, :, -1].zero_()
+            return
+        for m in self.model.modules():
+            if hasattr(m, "cache_rows") and m.k_cache.numel():
+                m.k_cache[-1].zero_()
+                m.v_cache[-1].zero_()
 
     # ------------------------------------------------------------------ run
     @torch.inference_mode()
-    def run(self, seqs: list[Sequence], is_prefill: bool) -> list[int] | None:
+    def run(self, seqs: list[Sequence], is_prefill: bool, logit_rows: list[int] | None = None):
+        """One step. Returns the sampled token of every sequence -- or, with ``logit_rows`` (scoring and trace
+        replay; Config.return_logits), nothing is sampled and the fp32 logits at those rows come back on the
+        host: rows index the step's packed tokens (a prefill-type step) or its sequences (a decode step)."""
         n = len(seqs)
+        if is_prefill and logit_rows is not None:
+            ids, pos = self.prepare_prefill(seqs)
+            hidden = self.model(ids, pos)
+            out = None
+            if logit_rows:
+                rows = torch.tensor(logit_rows, dtype=torch.int64, pin_memory=True).to(self.device, non_blocking=True)
+                out = self.model.lm_head.logits_at(hidden, rows).float().cpu()
+            reset_context()
+            return out
         if is_prefill:
             ids, pos = self.prepare_prefill(seqs)
             out = self.d_out[:n] if n <= self.d_out.numel() else torch.empty(
@@ -515,6 +615,8 @@ class ModelRunner:
                 reset_context()
                 return out.tolist()
             logits = self.model.compute_logits(self.model(ids, pos))
+            if logits is not None and logits.dtype == torch.float32:
+                logits = logits.to(torch.bfloat16)
             if self.rank == 0:
                 temps = torch.tensor([0.0 if s.greedy else s.temperature for s in seqs],
                                      dtype=torch.float32, pin_memory=True).to(self.device, non_blocking=True)
@@ -533,6 +635,11 @@ class ModelRunner:
             self._set_decode_context(bs, n)
             self._decode_step(bs, self.use_split(bs, kv_tokens))
             reset_context()
+        if logit_rows is not None:
+            if self.d_logits is None:
+                raise RuntimeError("logits of decode steps are kept only with Config.return_logits")
+            return self.d_logits[torch.tensor(logit_rows, dtype=torch.int64, device=self.device)].cpu() \
+                if logit_rows else None
         self.h_out[:n].copy_(self.d_out[:n], non_blocking=True)
         self.d2h_bytes += n * 8
         torch.cuda.current_stream().synchronize()

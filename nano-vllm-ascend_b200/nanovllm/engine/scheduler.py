@@ -18,7 +18,10 @@ class Scheduler:
         self.chunked_prefill = getattr(config, "chunked_prefill", False)
         # the last physical block is the dummy slot padded graph rows write to
         # (reference scheduler.py:26-30, model_runner.py:310)
-        self.block_manager = BlockManager(config.num_kvcache_blocks - 1, config.kvcache_block_size)
+        self.block_manager = BlockManager(config.num_kvcache_blocks - 1, config.kvcache_block_size,
+                                          num_state_slots=max(0, getattr(config, "num_state_slots", 0)),
+                                          prefix_caching=getattr(config, "enable_prefix_caching", True))
+        self.given: dict[str, Sequence] = {}         # sequences fed by schedule_given, by request id
         self.waiting: deque[Sequence] = deque()
         self.running: deque[Sequence] = deque()
 
@@ -50,6 +53,54 @@ class Scheduler:
         if batch:
             return batch, True
         return self._schedule_decode(), False
+
+    def schedule_given(self, entries: list[tuple[str, list[int]]]) -> tuple[list[Sequence], bool]:
+        """One step whose content the caller dictates instead of the queues: for every (request id, next
+        tokens) the sequence is admitted at its first entry (blocks + state slot from the block manager) or
+        extended, and gets a ``prefill_window`` over exactly these tokens. Returns (batch, is_prefill) like
+        ``schedule``: the step is a decode step when every entry is one token of an already-running sequence,
+        otherwise a packed step in which single tokens sit beside prompt portions. The sequences stay out of
+        ``waiting``/``running``; ``postprocess`` and ``finish_given`` complete the step."""
+        batch = []
+        if len(entries) > self.max_num_seqs:
+            raise RuntimeError(f"{len(entries)} sequences in one step, max_num_seqs is {self.max_num_seqs}")
+        for request_id, tokens in entries:
+            seq = self.given.get(request_id)
+            if seq is None:
+                seq = Sequence(tokens, request_id=request_id, block_size=self.block_manager.block_size)
+                seq.max_tokens = 1 << 62
+                seq.ignore_eos = True
+                if len(self.given) >= self.max_num_seqs or not self.block_manager.can_allocate(seq):
+                    raise RuntimeError("no blocks or state slot left to admit a sequence")
+                self.block_manager.allocate(seq)
+                seq.num_computed_tokens = 0
+                seq.status = SequenceStatus.RUNNING
+                self.given[request_id] = seq
+            else:
+                seq.extend_prompt(tokens)
+                if not self.block_manager.can_extend(seq):
+                    raise RuntimeError("no blocks left to extend a sequence")
+                self.block_manager.extend(seq)
+            if len(seq) > self.max_model_len:
+                raise RuntimeError(f"sequence of {len(seq)} tokens exceeds max_model_len {self.max_model_len}")
+            seq.prefill_window = (seq.num_computed_tokens, len(seq))
+            batch.append(seq)
+        decode = all(s.prefill_window[1] - s.prefill_window[0] == 1 and s.prefill_window[0] > 0 for s in batch)
+        if decode:
+            for s in batch:
+                s.prefill_window = None
+        return batch, not decode
+
+    def postprocess_given(self, seqs: list[Sequence]) -> None:
+        for seq in seqs:
+            seq.prefill_window = None
+            seq.num_computed_tokens = len(seq)
+
+    def finish_given(self, request_id: str) -> None:
+        seq = self.given.pop(request_id)
+        seq.status = SequenceStatus.FINISHED
+        seq.finish_reason = FinishReason.LENGTH
+        self.block_manager.deallocate(seq)
 
     def _schedule_prefill_chunks(self) -> list[Sequence]:
         """Chunked variant of step 1 (an extension; the reference admits whole prompts only). A prompt

@@ -41,6 +41,9 @@ class Sequence:
         # of the prompt the current prefill step computes (None = the whole prompt, reference behaviour)
         self.num_computed_tokens = 0
         self.prefill_window: tuple[int, int] | None = None
+        # hybrid models: the row of the per-sequence state pool (recurrent state, convolution tails) this
+        # sequence owns while it holds blocks; -1 = none (block_manager.allocate / deallocate)
+        self.state_slot = -1
         self.temperature = sp.temperature
         self.max_tokens = sp.max_tokens
         self.ignore_eos = sp.ignore_eos
@@ -92,6 +95,13 @@ class Sequence:
         self.last_token = token_id
         self.num_tokens += 1
 
+    def extend_prompt(self, token_ids: list[int]) -> None:
+        """More given tokens for a sequence that is fed step by step (Scheduler.schedule_given)."""
+        self.token_ids.extend(token_ids)
+        self.last_token = self.token_ids[-1]
+        self.num_tokens = len(self.token_ids)
+        self.num_prompt_tokens = self.num_tokens
+
     # state shipped to tensor-parallel workers each step. Unlike the reference
     # (sequence.py:116-146, SURVEY appendix A) block_size and the sampling fields travel too,
     # otherwise num_blocks raises on the worker side.
@@ -99,7 +109,7 @@ class Sequence:
     # the prompt travels as packed int32 bytes, and only while the sequence is still being prefilled.
     _WIRE = ("block_size", "seq_id", "num_tokens", "num_prompt_tokens", "num_cached_tokens",
              "last_token", "status", "temperature", "max_tokens",
-             "ignore_eos", "greedy", "num_computed_tokens", "prefill_window")
+             "ignore_eos", "greedy", "num_computed_tokens", "prefill_window", "state_slot")
     wire_decode = False          # set by ModelRunner.call around the pickling of a decode batch
 
     def __getstate__(self):

@@ -56,6 +56,12 @@ class ParallelLMHead(VocabParallelEmbedding):
             x = x[(context.cu_seqlens_q[1:] - 1).long()].contiguous()
         return F.linear(x, self.weight)
 
+    def logits_at(self, x, rows):
+        """Logits of the given rows of the step's hidden states (scoring: any position, not only the last)."""
+        if self.tp_size > 1:
+            raise NotImplementedError("logits at arbitrary rows are computed on one GPU")
+        return F.linear(x[rows].contiguous(), self.weight)
+
     def forward(self, x):
         context = get_context()
         if context.is_prefill:

@@ -546,3 +546,227 @@ def _moe_combine(lib, y, topk_ids, plan: MoePlan, T, hidden, out, x):
                                   out.stride(0) if T > 1 else hidden, _dt(x), _stream()),
              "b200_moe_combine")
     return out
+
+
+# ---------------------------------------------------------------------------------------------------
+# Sequence-mixer kernels of the hybrid decoders (csrc/seq_ops.cu, csrc/seq_mixers.cu). They take bf16,
+# fp16 and fp32 activations; small parameters (norm weights, convolution taps, decays) are fp32 tensors.
+_DT3 = {torch.bfloat16: _C.BF16, torch.float16: _C.F16, torch.float32: _C.F32}
+
+
+def _dt3(t: torch.Tensor) -> int:
+    try:
+        return _DT3[t.dtype]
+    except KeyError:
+        raise TypeError(f"sequence-mixer kernels take bf16/fp16/fp32 tensors, got {t.dtype}") from None
+
+
+def _f32(*tensors) -> None:
+    for t in tensors:
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous() or not t.is_cuda):
+            raise TypeError("small parameters of the sequence-mixer kernels are contiguous fp32 CUDA tensors")
+
+
+class StepSpans:
+    """Which tokens of the step belong to which sequence, as the kernels take it: packed spans
+    (``cu_q``/``cu_k``, any mix of prompt portions and single tokens) or one token per row
+    (``ctx_lens``; 0 = a padded graph row). Built from the runner's step context, or directly in tests."""
+    __slots__ = ("cu_q", "cu_k", "ctx_lens", "num_seqs", "max_q")
+
+    def __init__(self, cu_q=None, cu_k=None, ctx_lens=None, max_q=1):
+        if (cu_q is None) == (ctx_lens is None):
+            raise ValueError("give either cu_q/cu_k (packed spans) or ctx_lens (one token per row)")
+        for t in (cu_q, cu_k, ctx_lens):
+            if t is not None and (t.dtype != torch.int32 or not t.is_contiguous() or not t.is_cuda):
+                raise TypeError("span tensors are contiguous int32 CUDA tensors")
+        self.cu_q, self.cu_k, self.ctx_lens = cu_q, cu_k, ctx_lens
+        self.num_seqs = (cu_q.numel() - 1) if cu_q is not None else ctx_lens.numel()
+        self.max_q = int(max_q) if cu_q is not None else 1
+
+    @classmethod
+    def of(cls, context) -> "StepSpans":
+        if context.is_prefill:
+            return cls(context.cu_seqlens_q, context.cu_seqlens_k, None, context.max_seqlen_q)
+        return cls(None, None, context.context_lens)
+
+    def ptrs(self):
+        return _ptr(self.cu_q), _ptr(self.cu_k), _ptr(self.ctx_lens)
+
+
+def residual_rmsnorm(residual, weight, eps, dtype, offset=1.0):
+    """h = residual * rsqrt(mean(residual^2) + eps) * (offset + weight); residual fp32 [rows, hidden] -> h in `dtype`."""
+    _need_cuda(residual, weight)
+    _f32(residual, weight)
+    rows, hidden = residual.shape
+    out = torch.empty(rows, hidden, dtype=dtype, device=residual.device)
+    _C.check(_C.load().b200_residual_rmsnorm(out.data_ptr(), residual.data_ptr(), weight.data_ptr(), float(offset),
+                                             float(eps), rows, hidden, _dt3(out), _stream()),
+             "b200_residual_rmsnorm")
+    return out
+
+
+def residual_add_norms_(y, residual, w_post, w_pre, eps, offset=1.0):
+    """residual += norm(y; w_post) in place (fp32); returns h = norm(residual; w_pre) in y's dtype, or None when
+    w_pre is None. Both norms are x * rsqrt(mean x^2 + eps) * (offset + w)."""
+    _need_cuda(y, residual, w_post, w_pre)
+    _f32(residual, w_post, w_pre)
+    if not y.is_contiguous() or y.shape != residual.shape:
+        raise ValueError("y must be contiguous and shaped like the residual")
+    rows, hidden = residual.shape
+    h = torch.empty_like(y) if w_pre is not None else None
+    _C.check(_C.load().b200_residual_add_norms(_ptr(h), residual.data_ptr(), y.data_ptr(), w_post.data_ptr(),
+                                               _ptr(w_pre), float(offset), float(eps), rows, hidden, _dt3(y),
+                                               _stream()), "b200_residual_add_norms")
+    return h
+
+
+def causal_conv(x, weight, bias, spans: StepSpans, state=None, state_slots=None, act=None):
+    """Depth-wise causal convolution over time. x [T, C] (row-strided view allowed), weight fp32 [C, taps] (last
+    column = current token), bias fp32 [C] or None, act None | "silu". state [slots, taps-1, C] in x's dtype holds
+    each sequence's last taps-1 inputs between steps (read unless the span starts at position 0, then rewritten)."""
+    _need_cuda(x, weight, bias, state, state_slots)
+    _f32(weight, bias)
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise ValueError("x must be [T, C] with unit inner stride")
+    T, C = x.shape
+    taps = weight.shape[1]
+    if weight.shape[0] != C:
+        raise ValueError("one row of taps per channel")
+    if state is not None:
+        if state.dtype != x.dtype or not state.is_contiguous() or tuple(state.shape[1:]) != (taps - 1, C):
+            raise ValueError(f"conv state must be a contiguous [slots, {taps - 1}, {C}] tensor of x's dtype")
+        if state_slots is None or state_slots.dtype != torch.int32:
+            raise TypeError("state_slots must be int32")
+    out = torch.empty(T, C, dtype=x.dtype, device=x.device)
+    cu_q, cu_k, ctx = spans.ptrs()
+    _C.check(_C.load().b200_causal_conv(out.data_ptr(), C, x.data_ptr(), x.stride(0) if T > 1 else C,
+                                        weight.data_ptr(), _ptr(bias), 1 if act == "silu" else 0, _ptr(state),
+                                        _ptr(state_slots), cu_q, cu_k, ctx, spans.num_seqs, spans.max_q, C, taps,
+                                        _dt3(x), _stream()), "b200_causal_conv")
+    return out
+
+
+def unitnorm_temp_cache(qkv, positions, eps, temp_coef, temp_every, num_heads, num_kv_heads, dim, vdim,
+                        k_cache=None, v_cache=None, slots=None):
+    """In place on qkv [T, H*dim | G*dim | G*vdim]: every q and k head is divided by its root mean square, q is
+    then scaled by 1 + coef * ln(floor((pos + 1) / every) + 1); k and v rows are stored at `slots` of the paged
+    caches [nb, bs, G*dim] / [nb, bs, G*vdim] when those are given."""
+    _need_cuda(qkv, positions, k_cache, v_cache, slots)
+    T = qkv.shape[0]
+    if qkv.dim() != 2 or qkv.stride(1) != 1 or qkv.shape[1] != num_heads * dim + num_kv_heads * (dim + vdim):
+        raise ValueError("qkv must be [T, H*dim + G*dim + G*vdim] with unit inner stride")
+    if positions.dtype != torch.int64 or not positions.is_contiguous():
+        raise TypeError("positions must be contiguous int64")
+    have = k_cache is not None and k_cache.numel() > 0
+    bs = 0
+    if have:
+        _, bs = _cache_dims(k_cache, num_kv_heads * dim)
+        _cache_dims(v_cache, num_kv_heads * vdim)
+        if slots.dtype != torch.int32 or not slots.is_contiguous():
+            raise TypeError("slots must be contiguous int32")
+        if k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype:
+            raise TypeError("caches must have the activations' dtype")
+    _C.check(_C.load().b200_unitnorm_temp_cache(
+        qkv.data_ptr(), qkv.stride(0) if T > 1 else qkv.shape[1], positions.data_ptr(), float(eps),
+        float(temp_coef), int(temp_every), k_cache.data_ptr() if have else None,
+        v_cache.data_ptr() if have else None, slots.data_ptr() if have else None,
+        1 if (have and slots.dim() == 2) else 0, bs, T, num_heads, num_kv_heads, dim, vdim, _dt3(qkv), _stream()),
+        "b200_unitnorm_temp_cache")
+    return qkv
+
+
+def gated_norm(y, gate, weight, eps, groups=1, gate_first=False, gate_act="sigmoid"):
+    """y [rows, n] (fp32 or gate's dtype), gate [rows, n] (row-strided view allowed) -> [rows, n] in gate's dtype.
+    weight fp32 [n]: RMS norm over each of `groups` equal parts, before (gate_first=False) or after the gate;
+    weight None: the gate alone."""
+    _need_cuda(y, gate, weight)
+    _f32(weight)
+    rows, n = y.shape
+    if not y.is_contiguous() or gate.shape != y.shape or gate.stride(1) != 1:
+        raise ValueError("y contiguous [rows, n]; gate [rows, n] with unit inner stride")
+    if y.dtype not in (torch.float32, gate.dtype):
+        raise TypeError("y must be fp32 or of the gate's dtype")
+    out = torch.empty(rows, n, dtype=gate.dtype, device=gate.device)
+    _C.check(_C.load().b200_gated_norm(out.data_ptr(), y.data_ptr(), 1 if y.dtype == torch.float32 else 0,
+                                       gate.data_ptr(), gate.stride(0) if rows > 1 else n, _ptr(weight), float(eps),
+                                       rows, n, int(groups), 1 if gate_first else 0,
+                                       {"sigmoid": 0, "silu": 1}[gate_act], _dt3(gate), _stream()),
+             "b200_gated_norm")
+    return out
+
+
+_ACTS = {"silu": 0, "relu": 1, "gelu_tanh": 2}
+
+
+def act_and_mul(x, act="silu"):
+    """x [rows, 2*inter] = (gate | up) -> act(gate) * up, act in silu | relu | gelu_tanh."""
+    _need_cuda(x)
+    if not x.is_contiguous() or x.dim() != 2:
+        raise ValueError("act_and_mul input must be a contiguous matrix")
+    rows, inter = x.shape[0], x.shape[1] // 2
+    out = torch.empty(rows, inter, dtype=x.dtype, device=x.device)
+    _C.check(_C.load().b200_act_and_mul(out.data_ptr(), x.data_ptr(), rows, inter, _ACTS[act], _dt3(x), _stream()),
+             "b200_act_and_mul")
+    return out
+
+
+def attn_generic(q, k, v, spans: StepSpans, scale, num_kv_heads, vdim, block_tables=None):
+    """Causal softmax attention for any head sizes and dtypes. q [T, H, dim]; packed mode: k [Tk, G, dim],
+    v [Tk, G, vdim] (token-strided views allowed) in the order of spans.cu_k; paged mode (block_tables given):
+    k, v are the caches [nb, bs, G*dim], [nb, bs, G*vdim]. Returns [T, H*vdim]."""
+    _need_cuda(q, k, v, block_tables)
+    T, H, dim = q.shape
+    if q.stride(2) != 1 or q.stride(1) != dim:
+        raise ValueError("q must be contiguous in (heads, dim)")
+    G = num_kv_heads
+    if block_tables is not None:
+        if block_tables.dtype != torch.int32 or block_tables.stride(1) != 1:
+            raise TypeError("block_tables must be row-major int32")
+        _, bs = _cache_dims(k, G * dim)
+        _cache_dims(v, G * vdim)
+        ks, vs, bt_ptr, bt_stride = G * dim, G * vdim, block_tables.data_ptr(), block_tables.stride(0)
+    else:
+        if k.stride(2) != 1 or k.stride(1) != dim or v.stride(2) != 1 or v.stride(1) != vdim:
+            raise ValueError("k/v must be contiguous in (heads, dim)")
+        bs, bt_ptr, bt_stride = 0, None, 0
+        ks = k.stride(0) if k.shape[0] > 1 else G * dim
+        vs = v.stride(0) if v.shape[0] > 1 else G * vdim
+    out = torch.empty(T, H * vdim, dtype=q.dtype, device=q.device)
+    cu_q, cu_k, ctx = spans.ptrs()
+    _C.check(_C.load().b200_attn_generic(out.data_ptr(), q.data_ptr(), q.stride(0) if T > 1 else H * dim,
+                                         k.data_ptr(), ks, v.data_ptr(), vs, bt_ptr, bt_stride, bs, cu_q, cu_k, ctx,
+                                         spans.num_seqs, spans.max_q, H, G, dim, vdim, float(scale), _dt3(q),
+                                         _stream()), "b200_attn_generic")
+    return out
+
+
+def linear_recurrence(q, k, v, spans: StepSpans, num_heads, groups, kdim, vdim, state=None, state_slots=None,
+                      decay=None, act_silu=False, dt=None, dt_bias=None, a_log=None, d_skip=None):
+    """Per head S_t = a_t S_(t-1) + k_t (b_t v_t)^T, o_t = S_t^T q_t, S fp32 [kdim, vdim] carried in
+    state[slot] ([slots, H, kdim, vdim] fp32) between steps. q, k [T, groups*kdim] (head h reads group
+    h // (H / groups)), v [T, H*vdim]; row-strided views allowed. Returns fp32 [T, H*vdim].
+      decay given (fp32 [H]): a_t = decay_h, b_t = 1; act_silu applies silu to q, k, v as they are read.
+      dt given ([T, H]):      step = softplus(dt + dt_bias_h), a_t = exp(-exp(a_log_h) * step), b_t = step, and
+                              o_t += d_skip_h * v_t."""
+    _need_cuda(q, k, v, state, state_slots, decay, dt, dt_bias, a_log, d_skip)
+    _f32(decay, dt_bias, a_log, d_skip, state)
+    T = q.shape[0]
+    for t, n in ((q, groups * kdim), (k, groups * kdim), (v, num_heads * vdim)):
+        if t.dim() != 2 or t.shape[1] != n or t.stride(1) != 1 or t.dtype != q.dtype:
+            raise ValueError("q, k [T, groups*kdim] and v [T, H*vdim] with unit inner stride, one dtype")
+    if state is not None and tuple(state.shape[1:]) != (num_heads, kdim, vdim):
+        raise ValueError(f"state must be [slots, {num_heads}, {kdim}, {vdim}]")
+    if state is not None and (state_slots is None or state_slots.dtype != torch.int32):
+        raise TypeError("state_slots must be int32")
+    mode = 0 if decay is not None else 1
+    if mode == 1 and (dt is None or dt.shape != (T, num_heads) or dt.stride(1) != 1 or dt.dtype != q.dtype):
+        raise ValueError("dt must be [T, H] of q's dtype")
+    out = torch.empty(T, num_heads * vdim, dtype=torch.float32, device=q.device)
+    cu_q, cu_k, ctx = spans.ptrs()
+    stride = lambda t: t.stride(0) if T > 1 else t.shape[1]
+    _C.check(_C.load().b200_linear_recurrence(
+        out.data_ptr(), q.data_ptr(), stride(q), k.data_ptr(), stride(k), v.data_ptr(), stride(v), _ptr(state),
+        _ptr(state_slots), cu_q, cu_k, ctx, spans.num_seqs, num_heads, groups, kdim, vdim, mode,
+        1 if act_silu else 0, _ptr(decay), _ptr(dt), stride(dt) if dt is not None else 0, _ptr(dt_bias),
+        _ptr(a_log), _ptr(d_skip), _dt3(q), _stream()), "b200_linear_recurrence")
+    return out

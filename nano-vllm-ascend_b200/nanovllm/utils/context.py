@@ -20,6 +20,8 @@ Second addition: ``decode_attn_ctas`` -- persistent grid size of the paged decod
 half leaves SMs to the GEMMs of the other (engine/model_runner.py). Third: ``own_gemm`` -- the
 linear layers of this step run on the library's single-CTA tcgen05 GEMM (ops.linear_umma) instead of
 cuBLAS, whose 2-CTA clustered kernels cannot be placed next to a resident attention kernel.
+Fourth: ``state_slots`` -- int32 [num_seqs], the state slot of every sequence of the step (hybrid models:
+recurrent state and convolution tails live in per-slot rows; None for models without such state).
 """
 from __future__ import annotations
 
@@ -44,6 +46,7 @@ class Context:
     paged_prefill: bool = False
     decode_attn_ctas: int = 0
     own_gemm: bool = False
+    state_slots: torch.Tensor | None = None
 
 
 _current = Context()
@@ -55,11 +58,12 @@ def get_context() -> Context:
 
 def set_context(is_prefill, cu_seqlens_q=None, cu_seqlens_k=None, max_seqlen_q=0, max_seqlen_k=0,
                 slot_mapping=None, context_lens=None, block_tables=None, is_enforce_eager=None,
-                real_bs=None, block_size=None, paged_prefill=False, decode_attn_ctas=0, own_gemm=False) -> None:
+                real_bs=None, block_size=None, paged_prefill=False, decode_attn_ctas=0, own_gemm=False,
+                state_slots=None) -> None:
     global _current
     _current = Context(is_prefill, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
                        slot_mapping, context_lens, block_tables, is_enforce_eager, real_bs,
-                       block_size, paged_prefill, decode_attn_ctas, own_gemm)
+                       block_size, paged_prefill, decode_attn_ctas, own_gemm, state_slots)
 
 
 def reset_context() -> None:

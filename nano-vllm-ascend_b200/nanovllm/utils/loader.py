@@ -16,10 +16,19 @@ def load_model(model: nn.Module, path: str) -> int:
     from safetensors import safe_open
     packed = getattr(model, "packed_modules_mapping", {})
     elsewhere = getattr(model, "virtual_param_shapes", dict)()    # experts held by other ranks
+    route = getattr(model, "route_checkpoint_tensor", None)       # models with their own tensor names
     count = 0
     for file in sorted(glob(os.path.join(path, "*.safetensors"))):
         with safe_open(file, "pt", "cpu") as f:
             for name in f.keys():
+                if route is not None:
+                    target, shard_id = route(name)
+                    param = model.get_parameter(target)
+                    tensor = f.get_tensor(name).to(param.dtype)
+                    loader = getattr(param, "weight_loader", lambda p, w: p.data.copy_(w))
+                    loader(param, tensor) if shard_id is None else loader(param, tensor, shard_id)
+                    count += 1
+                    continue
                 fused_name = name
                 for key, (fused, _) in packed.items():
                     if key in name:
