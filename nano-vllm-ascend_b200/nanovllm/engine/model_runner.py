@@ -638,8 +638,11 @@ class ModelRunner:
         if logit_rows is not None:
             if self.d_logits is None:
                 raise RuntimeError("logits of decode steps are kept only with Config.return_logits")
-            return self.d_logits[torch.tensor(logit_rows, dtype=torch.int64, device=self.device)].cpu() \
-                if logit_rows else None
+            if not logit_rows:
+                # the next step refills the pinned staging buffer: this step's upload must have left it
+                torch.cuda.current_stream().synchronize()
+                return None
+            return self.d_logits[torch.tensor(logit_rows, dtype=torch.int64, device=self.device)].cpu()
         self.h_out[:n].copy_(self.d_out[:n], non_blocking=True)
         self.d2h_bytes += n * 8
         torch.cuda.current_stream().synchronize()
