@@ -102,6 +102,10 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--mem-util", type=float, default=0.7, help="gpu_memory_utilization of the engine")
     ap.add_argument("--cpu-sample-seqs", type=int, default=32)
+    ap.add_argument("--hybrid", action="store_true",
+                    help="instead of the contract workload: prefill and decode throughput of the Zegopel hybrid "
+                         "decoder beside the dense decoder of the same width and depth, and its kernels' rooflines")
+    ap.add_argument("--hybrid-pairs", default="zegopel-1k:qwen3-0.6b,zegopel-2k:llama-3.2-1b")
     ap.add_argument("--kv-cache-dtype", default="auto", choices=["auto", "fp8"],
                     help="fp8: e4m3 KV cache (an extra line; the contract line is the default bf16 cache)")
     return ap.parse_args()
@@ -598,8 +602,153 @@ def tp_block(args, rank, world, K, W, peak, peak_src):
     return out
 
 
+def _timed(fn, flush, reps=5):
+    """Median CUDA-event time (s) of fn() with L2 flushed (a 256 MB write) before every launch."""
+    out = []
+    for i in range(reps + 2):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        if i >= 2:
+            out.append(e0.elapsed_time(e1) / 1e3)
+    return statistics.median(out)
+
+
+def hybrid_kernel_table(width, head_dim, tokens, seqs, peak_gbs):
+    """The row-wise and mixer kernels of the hybrid decoder alone, at the layer sizes of a `width`-wide model, as a
+    prompt step (`seqs` x tokens/seqs) and as a decode step (`seqs` rows at that context), each beside the dense
+    decoders' kernel that does the like job. frac = algorithmic bytes / time / measured copy bandwidth."""
+    from nanovllm import ops
+    dev, bf = "cuda", torch.bfloat16
+    g = torch.Generator(device=dev).manual_seed(0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    rnd = lambda *shape: torch.randn(*shape, device=dev, generator=g)
+    H = width // head_dim
+    G = max(1, H // 4)
+    rows = []
+
+    def add(name, step, fn, nbytes, like=None, like_fn=None, like_bytes=None, flops=None):
+        t = _timed(fn, flush)
+        row = {"kernel": name, "step": step, "us": round(t * 1e6, 1), "GB/s": round(nbytes / t / 1e9),
+               "frac_of_measured_copy": round(nbytes / t / 1e9 / peak_gbs, 3)}
+        if flops:
+            row["TFLOP/s_fp32"] = round(flops / t / 1e12, 2)
+        if like_fn is not None:
+            tl = _timed(like_fn, flush)
+            row["like"] = {"kernel": like, "us": round(tl * 1e6, 1),
+                           "frac_of_measured_copy": round(like_bytes / tl / 1e9 / peak_gbs, 3)}
+        rows.append(row)
+
+    for step, T, spans_of in (("prompt", tokens, None), ("decode", seqs, None)):
+        per = T // seqs if step == "prompt" else 1
+        ctx = tokens // seqs
+        if step == "prompt":
+            cu = torch.arange(0, T + 1, per, dtype=torch.int32, device=dev)
+            spans = ops.StepSpans(cu, cu, None, per)
+        else:
+            spans = ops.StepSpans(None, None, torch.full((T,), ctx, dtype=torch.int32, device=dev))
+        slots = torch.arange(seqs, dtype=torch.int32, device=dev)
+        # residual path
+        y, res = rnd(T, width).to(bf), rnd(T, width)
+        w1, w2 = rnd(width) * 0.1, rnd(width) * 0.1
+        xb, rb, wb = rnd(T, width).to(bf), rnd(T, width).to(bf), rnd(width).to(bf)
+        add("residual_add_norms", step, lambda: ops.residual_add_norms_(y, res, w1, w2, 1e-6), T * width * 12,
+            "add_rmsnorm", lambda: ops.add_rmsnorm_(xb, rb, wb, 1e-6), T * width * 8)
+        ff = 3 * width
+        gu = rnd(T, 2 * ff).to(bf)
+        add("act_and_mul(relu)", step, lambda: ops.act_and_mul(gu, "relu"), T * ff * 6,
+            "silu_and_mul", lambda: ops.silu_and_mul(gu), T * ff * 6)
+        # attention mixer epilogue: convolution, then unit norms + temperature + scatter
+        nq, nk = H * head_dim, G * head_dim
+        C = nq + 2 * nk
+        proj = rnd(T, C + nq).to(bf)
+        cw = rnd(C, 3)
+        cstate = torch.zeros(seqs + 1, 2, C, dtype=bf, device=dev)
+        add("causal_conv(q|k|v, 3 taps)", step,
+            lambda: ops.causal_conv(proj[:, :C], cw, None, spans, cstate, slots), T * C * 4)
+        qkv = rnd(T, C).to(bf)
+        pos = torch.arange(T, device=dev) % max(per, 1) + (0 if step == "prompt" else ctx - 1)
+        nb = (T + 15) // 16 + 1
+        kc = torch.zeros(nb, 16, nk, dtype=bf, device=dev)
+        vc = torch.zeros(nb, 16, nk, dtype=bf, device=dev)
+        sl = torch.arange(T, dtype=torch.int32, device=dev)
+        table = torch.cat([torch.cos(rnd(4096, head_dim // 2)), torch.sin(rnd(4096, head_dim // 2))], -1).contiguous()
+        qw = torch.ones(head_dim, dtype=bf, device=dev)
+        like_pos = pos.clamp(max=4095)
+        add("unitnorm_temp_cache", step,
+            lambda: ops.unitnorm_temp_cache(qkv, pos, 1e-6, 0.1, 1024, H, G, head_dim, head_dim, kc, vc, sl),
+            T * (2 * (nq + nk) * 2 + nk * 2 + 2 * nk * 2),
+            "qknorm_rope_cache", lambda: ops.qknorm_rope_cache(qkv, like_pos, table, qw, qw, 1e-6, kc, vc, sl, H, G, head_dim),
+            T * (2 * (nq + nk) * 2 + nk * 2 + 2 * nk * 2))
+        o32, gate = rnd(T, nq), rnd(T, 2 * nq).to(bf)
+        nw = rnd(nq)
+        add("gated_norm(norm, sigmoid gate)", step, lambda: ops.gated_norm(o32, gate[:, nq:], nw, 1e-6), T * nq * 8)
+        # recurrences: lightning (H heads of head_dim x head_dim) and the selective form (2*width/64 heads, state 128)
+        p4 = rnd(T, 4 * nq).to(bf)
+        decay = torch.linspace(0.9, 0.999, H, device=dev)
+        st = torch.zeros(seqs + 1, H, head_dim, head_dim, device=dev)
+        rec_bytes = T * nq * (3 * 2 + 4) + (2 * seqs * H * head_dim * head_dim * 4 if step == "decode" else 0)
+        add("linear_recurrence(constant decay)", step,
+            lambda: ops.linear_recurrence(p4[:, :nq], p4[:, nq:2 * nq], p4[:, 2 * nq:3 * nq], spans, H, H, head_dim,
+                                          head_dim, st, slots, decay=decay, act_silu=True),
+            rec_bytes, flops=4.0 * T * H * head_dim * head_dim)
+        Hm, dvm, N, Gm = 2 * width // 64, 64, 128, 8
+        xbc = rnd(T, Hm * dvm + 2 * Gm * N).to(bf)
+        dt = rnd(T, Hm).to(bf)
+        stm = torch.zeros(seqs + 1, Hm, N, dvm, device=dev)
+        par = [rnd(Hm) * 0.5, -torch.rand(Hm, device=dev, generator=g) * 2, torch.ones(Hm, device=dev)]
+        inner = Hm * dvm
+        add("linear_recurrence(selective)", step,
+            lambda: ops.linear_recurrence(xbc[:, inner + Gm * N:], xbc[:, inner:inner + Gm * N], xbc[:, :inner], spans,
+                                          Hm, Gm, N, dvm, stm, slots, dt=dt, dt_bias=par[0], a_log=par[1], d_skip=par[2]),
+            T * (inner * 6 + 2 * Gm * N * 2) + (2 * seqs * Hm * N * dvm * 4 if step == "decode" else 0),
+            flops=4.0 * T * Hm * N * dvm)
+    return rows
+
+
+def hybrid_compare(args):
+    """--hybrid: the Zegopel presets beside the dense presets of the same width and depth, each through the engine
+    (LLM.add_request / LLM.step; prompt steps, then CUDA-graph decode steps), plus the kernel table."""
+    from nanovllm import LLM
+    K, W, B, ctx = min(args.steps, 64), max(3, args.warmup), min(args.batch, 64), args.ctx
+    peak, peak_src = peaks()
+    clocks = ClockSampler(0)
+    clocks.start()
+    clocks.begin()
+    out = {"metric": "hybrid_vs_dense_tokens_per_s", "unit": UNIT, "n_gpus": 1, "steps": K, "warmup": W,
+           "dtype": "bf16", "data": "synthetic (random-init weights, random token ids)",
+           "config": {"batch": B, "ctx": ctx, "block_size": args.block_size, "l2": "prompts and caches exceed L2; "
+                      "kernel table: 256 MB flush before every timed launch"}, "models": [], "peak_source": peak_src}
+    for pair in args.hybrid_pairs.split(","):
+        for name in pair.split(":"):
+            llm = LLM(name, kvcache_block_size=args.block_size, max_num_seqs=B, max_model_len=max(4096, ctx + W + K + 16),
+                      max_num_batched_tokens=16384, gpu_memory_utilization=args.mem_util, seed=0)
+            r = decode_workload(llm, Group(1), B, ctx, K, W, 0, 0)
+            n_params = sum(p.numel() for p in llm.model_runner.model.parameters())
+            out["models"].append({"model": name, "parameters_M": round(n_params / 1e6),
+                                  "prefill_tokens_per_s": round(B * ctx / (sum(r["prefill_step_ms"]) / 1e3)),
+                                  "prefill_steps": r["prefill_steps"],
+                                  "decode_tokens_per_s": round(B * K / r["dev_s"]),
+                                  "decode_ms_per_step": round(r["dev_s"] / K * 1e3, 3),
+                                  "e2e_decode_tokens_per_s": round(B * K / r["e2e_s"]),
+                                  "gpu_launches_per_step": r["launches"] // K})
+            release(llm)
+            del llm
+            torch.cuda.empty_cache()
+    out["kernels"] = {"width_1024_head_128": hybrid_kernel_table(1024, 128, 16384, 16, peak),
+                      "width_2048_head_64": hybrid_kernel_table(2048, 64, 16384, 16, peak)}
+    out["clocks"] = clocks.stop()
+    print(json.dumps(out))
+
+
 def main():
     args = parse_args()
+    if args.hybrid:
+        hybrid_compare(args)
+        return
     if os.environ.get("B200_BENCH_DEBUG"):
         import faulthandler
         faulthandler.dump_traceback_later(int(os.environ["B200_BENCH_DEBUG"]), exit=True)

@@ -112,11 +112,15 @@ attn_generic_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_stri
 }
 
 // ------------------------------------------------------------------ linear recurrence with an fp32 state
-// CTA = 128 threads = 32 value columns x 4 key slices of one (sequence, head). Thread (slice ks, column j)
-// keeps S[ks + 4 r][j], r < KS, in registers; the 4 slices of a column sit in one warp (lanes l, l+8, l+16,
-// l+24), so o_t[j] is two shuffles. Tokens are staged kRecTok at a time in shared memory.
+// One CTA = 128 threads works on one (sequence, head) and a band of value columns. A thread owns ONE value column
+// and KPT <= 64 key rows of the state in registers (all rows when kdim <= 64; 2 or 4 adjacent lanes share a column
+// above that, one or two shuffles per token). Per token it reads k and q as float4 broadcasts from shared memory -- every lane of a warp reads the same
+// address -- and its own value, and does KPT updates S <- a S + k v and KPT output terms: the loop is fp32-issue
+// bound, and state rows are read and written as full 128-byte
+// lines (lanes = consecutive columns). Key rows past kdim and columns past vdim are zero-padded in shared memory,
+// so the inner loop has no bounds tests. Tokens are staged kRecTok at a time; the next batch is fetched into
+// registers while the current one is consumed.
 constexpr int kRecTok = 8;
-constexpr int kRecCols = 32;
 
 struct RecParams {
   const void *q, *k, *v;            // element type T; q, k: [tokens, groups * kdim]; v: [tokens, H * vdim]
@@ -133,113 +137,165 @@ struct RecParams {
   const float *dt_bias, *a_log, *d_skip;   // mode 1: [H] each
 };
 
-template <typename T, int KS>
+template <typename T, int KPT, int NS>
 __global__ void __launch_bounds__(128)
 linear_recurrence_kernel(const RecParams P) {
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   pdl_wait();
+  constexpr int KS = KPT;                            // slice stride (padding it against the 2-way bank conflict of
+                                                     // the NS broadcasts cost more in index arithmetic than it saved)
+  constexpr int KP = NS * KS;                        // row of padded keys
+  constexpr int CC = 128 / NS;                       // value columns per CTA
   const int s = blockIdx.z, h = blockIdx.y;
   const SeqSpan sp = seq_span(P.cu_q, P.cu_k, P.ctx_lens, s);
   if (sp.q_len == 0) return;
   const int kdim = P.kdim, vdim = P.vdim;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int ks = lane >> 3, jl = warp * 8 + (lane & 7);
-  const int j = blockIdx.x * kRecCols + jl;
-  const bool col_ok = j < vdim;
+  const int ksl = threadIdx.x % NS;                  // key slice: rows ksl*KPT .. ksl*KPT + KPT - 1
+  const int cl = threadIdx.x / NS;                   // column within the CTA's band
+  const int c0 = blockIdx.x * CC;                    // first column of the band
+  const int col = c0 + cl;
+  const bool col_ok = col < vdim;
+  // a warp none of whose columns exist only helps with the staging (warp-uniform, so shuffles stay legal)
+  const bool warp_live = c0 + (int)((threadIdx.x & ~31u) / NS) < vdim;
   const int grp = h / (P.H / P.groups);
-  float* sq = smem;                                  // [kRecTok][kdim]
-  float* skk = sq + kRecTok * kdim;                  // [kRecTok][kdim]
-  float* sx = skk + kRecTok * kdim;                  // [kRecTok][kRecCols] values of this CTA's columns
-  float* sa = sx + kRecTok * kRecCols;               // [kRecTok] decay of the step
+  float* sq = smem;                                  // [kRecTok][KP]
+  float* skk = sq + kRecTok * KP;                    // [kRecTok][KP]
+  float* sx = skk + kRecTok * KP;                    // [kRecTok][CC]
+  float* sa = sx + kRecTok * CC;                     // [kRecTok] decay of the step
   float* sdt = sa + kRecTok;                         // [kRecTok] step size (1 for a constant decay)
 
-  float S[KS];
+  float S[KPT];
   float* slot = P.state != nullptr
                     ? P.state + (((int64_t)P.state_slots[s] * P.H + h) * kdim) * (int64_t)vdim
                     : nullptr;
   const bool carried = slot != nullptr && sp.first_pos() > 0;
 #pragma unroll
-  for (int r = 0; r < KS; ++r) {
-    const int i = ks + 4 * r;
-    S[r] = (carried && col_ok && i < kdim) ? slot[(int64_t)i * vdim + j] : 0.f;
+  for (int r = 0; r < KPT; ++r) {
+    const int i = ksl * KPT + r;
+    S[r] = (carried && col_ok && i < kdim) ? slot[(int64_t)i * vdim + col] : 0.f;
   }
-  const T* q = (const T*)P.q;
-  const T* k = (const T*)P.k;
-  const T* v = (const T*)P.v;
+  const T* q = (const T*)P.q + (int64_t)grp * kdim;
+  const T* k = (const T*)P.k + (int64_t)grp * kdim;
+  const T* v = (const T*)P.v + (int64_t)h * vdim + c0;
   const T* dt = (const T*)P.dt;
   const float a_const = P.mode == 0 ? P.decay[h] : 0.f;
   const float rate = P.mode == 1 ? expf(P.a_log[h]) : 0.f;
   const float dt_b = P.mode == 1 ? P.dt_bias[h] : 0.f;
   const float d_skip = P.mode == 1 ? P.d_skip[h] : 0.f;
+  const int vcols = min(CC, vdim - c0);
 
-  for (int t0 = 0; t0 < sp.q_len; t0 += kRecTok) {
+  constexpr int NQ = (kRecTok * KP + 127) / 128;     // q (and k) elements per thread per batch
+  constexpr int NV = kRecTok * CC / 128;
+  T pq[NQ], pk[NQ], pv[NV], pdt = from_f32<T>(0.f);
+  auto fetch = [&](int t0) {
     const int nt = min(kRecTok, sp.q_len - t0);
-    __syncthreads();
-    for (int e = threadIdx.x; e < nt * kdim; e += blockDim.x) {
-      const int tt = e / kdim, i = e - tt * kdim;
-      const int64_t tok = sp.q_start + t0 + tt;
-      float qv = to_f32<T>(q[tok * P.q_stride + (int64_t)grp * kdim + i]);
-      float kv = to_f32<T>(k[tok * P.k_stride + (int64_t)grp * kdim + i]);
-      if (P.act_silu) qv = silu_f(qv), kv = silu_f(kv);
-      sq[tt * kdim + i] = qv;
-      skk[tt * kdim + i] = kv;
+    const int64_t tok0 = sp.q_start + t0;
+#pragma unroll
+    for (int n = 0; n < NQ; ++n) {
+      const int e = threadIdx.x + n * 128;
+      const int tt = e / KP, w = e % KP;
+      const int i = (w / KS) * KPT + w % KS;              // key row of this shared-memory word (padding: none)
+      const bool ok = tt < nt && w % KS < KPT && i < kdim;
+      pq[n] = ok ? q[(tok0 + tt) * P.q_stride + i] : from_f32<T>(0.f);
+      pk[n] = ok ? k[(tok0 + tt) * P.k_stride + i] : from_f32<T>(0.f);
+    }
+#pragma unroll
+    for (int n = 0; n < NV; ++n) {
+      const int e = threadIdx.x + n * 128;
+      const int tt = e / CC, c = e % CC;
+      pv[n] = (tt < nt && c < vcols) ? v[(tok0 + tt) * P.v_stride + c] : from_f32<T>(0.f);
+    }
+    if (P.mode == 1 && threadIdx.x < nt) pdt = dt[(tok0 + threadIdx.x) * P.dt_stride + h];
+  };
+  auto stage = [&](int t0) {                         // registers -> shared memory, activations applied once
+    const int nt = min(kRecTok, sp.q_len - t0);
+#pragma unroll
+    for (int n = 0; n < NQ; ++n) {
+      const int e = threadIdx.x + n * 128;
+      float qv = to_f32<T>(pq[n]), kv = to_f32<T>(pk[n]);
+      if (P.act_silu) qv = silu_f(qv), kv = silu_f(kv);           // silu(0) = 0: the padding stays zero
+      if (e < kRecTok * KP) {
+        sq[e] = qv;
+        skk[e] = kv;
+      }
+    }
+#pragma unroll
+    for (int n = 0; n < NV; ++n) {
+      const int e = threadIdx.x + n * 128;
+      float x = to_f32<T>(pv[n]);
+      if (P.act_silu) x = silu_f(x);
+      sx[e] = x;
     }
     if (threadIdx.x < nt) {
       float a = a_const, step = 1.f;
       if (P.mode == 1) {
-        step = softplus_f(to_f32<T>(dt[(int64_t)(sp.q_start + t0 + threadIdx.x) * P.dt_stride + h]) + dt_b);
+        step = softplus_f(to_f32<T>(pdt) + dt_b);
         a = expf(-rate * step);
       }
       sa[threadIdx.x] = a;
       sdt[threadIdx.x] = step;
     }
-    for (int e = threadIdx.x; e < nt * kRecCols; e += blockDim.x) {
-      const int tt = e / kRecCols, c = e - tt * kRecCols;
-      const int col = blockIdx.x * kRecCols + c;
-      float x = 0.f;
-      if (col < vdim) x = to_f32<T>(v[(int64_t)(sp.q_start + t0 + tt) * P.v_stride + (int64_t)h * vdim + col]);
-      if (P.act_silu) x = silu_f(x);
-      sx[tt * kRecCols + c] = x;
-    }
+  };
+
+  fetch(0);
+  for (int t0 = 0; t0 < sp.q_len; t0 += kRecTok) {
+    const int nt = min(kRecTok, sp.q_len - t0);
+    __syncthreads();                                 // the previous batch has been consumed
+    stage(t0);
     __syncthreads();
+    if (t0 + kRecTok < sp.q_len) fetch(t0 + kRecTok);
+    if (!warp_live) continue;
+    float* outp = P.out + (int64_t)(sp.q_start + t0) * ((int64_t)P.H * vdim) + (int64_t)h * vdim + col;
     for (int tt = 0; tt < nt; ++tt) {
-      const float a = sa[tt], vj = sx[tt * kRecCols + jl] * sdt[tt];
-      const float* qt = sq + tt * kdim;
-      const float* kt = skk + tt * kdim;
-      float o = 0.f;
+      const float a = sa[tt], x = sx[tt * CC + cl], vj = x * sdt[tt];
+      const float4* q4 = reinterpret_cast<const float4*>(sq + tt * KP + ksl * KS);
+      const float4* k4 = reinterpret_cast<const float4*>(skk + tt * KP + ksl * KS);
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-      for (int r = 0; r < KS; ++r) {
-        const int i = ks + 4 * r;
-        if (i < kdim) {
-          S[r] = a * S[r] + kt[i] * vj;
-          o += S[r] * qt[i];
-        }
+      for (int r4 = 0; r4 < KPT / 4; ++r4) {
+        const float4 kq = k4[r4], qq = q4[r4];
+        S[r4 * 4 + 0] = a * S[r4 * 4 + 0] + kq.x * vj;
+        o0 += S[r4 * 4 + 0] * qq.x;
+        S[r4 * 4 + 1] = a * S[r4 * 4 + 1] + kq.y * vj;
+        o1 += S[r4 * 4 + 1] * qq.y;
+        S[r4 * 4 + 2] = a * S[r4 * 4 + 2] + kq.z * vj;
+        o2 += S[r4 * 4 + 2] * qq.z;
+        S[r4 * 4 + 3] = a * S[r4 * 4 + 3] + kq.w * vj;
+        o3 += S[r4 * 4 + 3] * qq.w;
       }
-      o += __shfl_xor_sync(0xffffffffu, o, 8);
-      o += __shfl_xor_sync(0xffffffffu, o, 16);
-      if (ks == 0 && col_ok) {
-        if (P.mode == 1) o += d_skip * sx[tt * kRecCols + jl];
-        P.out[(int64_t)(sp.q_start + t0 + tt) * ((int64_t)P.H * vdim) + (int64_t)h * vdim + j] = o;
+      float o = (o0 + o1) + (o2 + o3);
+#pragma unroll
+      for (int off = 1; off < NS; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+      if (ksl == 0 && col_ok) {
+        if (P.mode == 1) o += d_skip * x;
+        outp[(int64_t)tt * ((int64_t)P.H * vdim)] = o;
       }
     }
   }
   if (slot != nullptr && col_ok) {
 #pragma unroll
-    for (int r = 0; r < KS; ++r) {
-      const int i = ks + 4 * r;
-      if (i < kdim) slot[(int64_t)i * vdim + j] = S[r];
+    for (int r = 0; r < KPT; ++r) {
+      const int i = ksl * KPT + r;
+      if (i < kdim) slot[(int64_t)i * vdim + col] = S[r];
     }
   }
 }
 
+template <typename T, int KPT, int NS>
+static void recurrence_launch_as(const RecParams& P, int num_seqs, cudaStream_t stream) {
+  constexpr int CC = 128 / NS;
+  const dim3 grid((P.vdim + CC - 1) / CC, P.H, num_seqs);
+  const size_t smem = (size_t)(2 * kRecTok * NS * KPT + kRecTok * CC + 2 * kRecTok) * sizeof(float);
+  launch_pdl(linear_recurrence_kernel<T, KPT, NS>, grid, dim3(128), smem, stream, P);
+}
+
 template <typename T>
 static int recurrence_launch(const RecParams& P, int num_seqs, cudaStream_t stream) {
-  const dim3 grid((P.vdim + kRecCols - 1) / kRecCols, P.H, num_seqs);
-  const size_t smem = (size_t)(2 * kRecTok * P.kdim + kRecTok * kRecCols + 2 * kRecTok) * sizeof(float);
-  if (P.kdim <= 32) launch_pdl(linear_recurrence_kernel<T, 8>, grid, dim3(128), smem, stream, P);
-  else if (P.kdim <= 64) launch_pdl(linear_recurrence_kernel<T, 16>, grid, dim3(128), smem, stream, P);
-  else if (P.kdim <= 128) launch_pdl(linear_recurrence_kernel<T, 32>, grid, dim3(128), smem, stream, P);
-  else launch_pdl(linear_recurrence_kernel<T, 64>, grid, dim3(128), smem, stream, P);
+  if (P.kdim <= 16) recurrence_launch_as<T, 16, 1>(P, num_seqs, stream);
+  else if (P.kdim <= 32) recurrence_launch_as<T, 32, 1>(P, num_seqs, stream);
+  else if (P.kdim <= 64) recurrence_launch_as<T, 64, 1>(P, num_seqs, stream);
+  else if (P.kdim <= 128) recurrence_launch_as<T, 64, 2>(P, num_seqs, stream);
+  else recurrence_launch_as<T, 64, 4>(P, num_seqs, stream);
   return finish_launch();
 }
 

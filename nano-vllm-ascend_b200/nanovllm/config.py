@@ -71,6 +71,8 @@ def preset_hf_config(name: str):
     key = name.lower().rstrip("/").split("/")[-1]
     if key == "zegopel-1k":          # 28 layers at width 1024: the size class of qwen3-0.6b
         return NativeConfig(zegopel_preset(1024, "almlalm", 4, vocab=151936))
+    if key == "zegopel-2k":          # 16 layers at width 2048, head size 64: the size class of llama-3.2-1b
+        return NativeConfig(zegopel_preset(2048, "alml", 4, vocab=128256, head_dim=64))
     if key == "tiny-zegopel":
         return NativeConfig(zegopel_preset(128, "alm", 1, vocab=512, head_dim=32))
     if key == "qwen3-0.6b":
