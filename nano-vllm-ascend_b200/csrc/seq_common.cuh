@@ -60,6 +60,34 @@ __device__ __forceinline__ float cta_sum(float v, float* red) {
   return warp_sum(t);
 }
 
+// 8 consecutive elements <-> fp32 registers (16 bytes of a 16-bit type, 32 bytes of fp32); p 16-byte aligned
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&f)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = unpack2<T>(w[i]);
+    f[2 * i] = t.x, f[2 * i + 1] = t.y;
+  }
+}
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float (&f)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  f[0] = a.x, f[1] = a.y, f[2] = a.z, f[3] = a.w, f[4] = b.x, f[5] = b.y, f[6] = b.z, f[7] = b.w;
+}
+template <typename T>
+__device__ __forceinline__ void store8(T* p, const float (&f)[8]) {
+  uint4 u;
+  u.x = pack2<T>(f[0], f[1]), u.y = pack2<T>(f[2], f[3]), u.z = pack2<T>(f[4], f[5]), u.w = pack2<T>(f[6], f[7]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+template <>
+__device__ __forceinline__ void store8<float>(float* p, const float (&f)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(f[4], f[5], f[6], f[7]);
+}
+
 #define B200_DISPATCH_3(dtype, T, ...)                    \
   do {                                                    \
     if ((dtype) == B200_DTYPE_BF16) {                     \

@@ -61,6 +61,65 @@ residual_add_norms_kernel(T* __restrict__ h, float* __restrict__ res, const T* _
     o[i] = from_f32<T>(row[i] * rstd2 * (offset + w_pre[i]));
 }
 
+// 16-byte form of the two kernels above (hidden % 8 == 0): a thread keeps its 8-element vectors of the row in
+// registers (up to kResVecs per thread, 256 threads: hidden <= 8192), so the row is read once. The CTA has one
+// thread per vector up to 256, so that narrow rows do not idle half of it.
+constexpr int kResVecs = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+residual_add_norms_vec_kernel(T* __restrict__ h, float* __restrict__ res, const T* __restrict__ y,
+                              const float* __restrict__ w_post, const float* __restrict__ w_pre, float offset,
+                              float eps, int hidden) {
+  __shared__ float red[32];
+  pdl_wait();
+  const int nvec = hidden / 8;
+  const T* yr = y + (int64_t)blockIdx.x * hidden;
+  float* r = res + (int64_t)blockIdx.x * hidden;
+  float val[kResVecs][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int n = 0; n < kResVecs; ++n) {
+    const int vi = threadIdx.x + n * blockDim.x;
+    if (vi < nvec) {
+      load8<T>(yr + vi * 8, val[n]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += val[n][e] * val[n][e];
+    }
+  }
+  const float rstd = 1.0f / sqrtf(cta_sum(ss, red) / (float)hidden + eps);
+  float ss2 = 0.f;
+#pragma unroll
+  for (int n = 0; n < kResVecs; ++n) {
+    const int vi = threadIdx.x + n * blockDim.x;
+    if (vi < nvec) {
+      float rv[8], wv[8];
+      load8<float>(r + vi * 8, rv);
+      load8<float>(w_post + vi * 8, wv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        val[n][e] = rv[e] + val[n][e] * rstd * (offset + wv[e]);
+        ss2 += val[n][e] * val[n][e];
+      }
+      store8<float>(r + vi * 8, val[n]);
+    }
+  }
+  if (w_pre == nullptr) return;
+  const float rstd2 = 1.0f / sqrtf(cta_sum(ss2, red) / (float)hidden + eps);
+  T* o = h + (int64_t)blockIdx.x * hidden;
+#pragma unroll
+  for (int n = 0; n < kResVecs; ++n) {
+    const int vi = threadIdx.x + n * blockDim.x;
+    if (vi < nvec) {
+      float wv[8], ov[8];
+      load8<float>(w_pre + vi * 8, wv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ov[e] = val[n][e] * rstd2 * (offset + wv[e]);
+      store8<T>(o + vi * 8, ov);
+    }
+  }
+}
+
 // ------------------------------------------------------------------ causal convolution over time
 // out[t, c] = act(bias[c] + sum_j w[c, j] * u[t - taps + 1 + j, c]), u = 0 before the sequence's start.
 // The last taps-1 inputs of every sequence live in state[slot] as [taps-1, C] (oldest first) between steps.
@@ -125,6 +184,88 @@ causal_conv_kernel(T* __restrict__ out, int64_t out_stride, const T* __restrict_
   }
 }
 
+// 16-byte form (channels, strides % 8 == 0): one thread = 8 channels x kConvSeg tokens, same ownership of the tail
+template <typename T, int MT>
+__global__ void __launch_bounds__(128)
+causal_conv_vec_kernel(T* __restrict__ out, int64_t out_stride, const T* __restrict__ x, int64_t x_stride,
+                       const float* __restrict__ w, const float* __restrict__ bias, int act, T* __restrict__ state,
+                       const int* __restrict__ state_slots, const int* __restrict__ cu_q,
+                       const int* __restrict__ cu_k, const int* __restrict__ ctx_lens, int C, int taps) {
+  pdl_wait();
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  const int s = blockIdx.z;
+  const SeqSpan sp = seq_span(cu_q, cu_k, ctx_lens, s);
+  const int t0 = blockIdx.y * kConvSeg;
+  if (c >= C || t0 >= sp.q_len) return;
+  const int hist = taps - 1;
+  const bool carried = state != nullptr && sp.first_pos() > 0;
+  T* tail = state != nullptr ? state + (int64_t)state_slots[s] * hist * C : nullptr;
+  float wt[MT][8], b[8];
+#pragma unroll
+  for (int j = 0; j < MT; ++j)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) wt[j][e] = j < taps ? w[(int64_t)(c + e) * taps + j] : 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) b[e] = bias != nullptr ? bias[c + e] : 0.f;
+  auto input = [&](int i, float (&f)[8]) {
+    if (i >= 0) {
+      load8<T>(x + (int64_t)(sp.q_start + i) * x_stride + c, f);
+    } else if (carried) {
+      load8<T>(tail + (int64_t)(hist + i) * C + c, f);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = 0.f;
+    }
+  };
+  float win[MT][8];
+#pragma unroll
+  for (int j = 0; j < MT; ++j) {
+    if (j >= 1 && j < taps) {
+      input(t0 - taps + j, win[j]);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) win[j][e] = 0.f;
+    }
+  }
+  const int t1 = min(t0 + kConvSeg, sp.q_len);
+  for (int t = t0; t < t1; ++t) {
+    float cur[8], acc[8];
+    input(t, cur);
+#pragma unroll
+    for (int j = 0; j < MT - 1; ++j)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) win[j][e] = win[j + 1][e];
+#pragma unroll
+    for (int j = 0; j < MT; ++j)
+      if (j == taps - 1) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) win[j][e] = cur[e];
+      }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = b[e];
+#pragma unroll
+    for (int j = 0; j < MT; ++j)
+      if (j < taps) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += wt[j][e] * win[j][e];
+      }
+    if (act == 1) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = silu_f(acc[e]);
+    }
+    store8<T>(out + (int64_t)(sp.q_start + t) * out_stride + c, acc);
+  }
+  if (t0 == 0 && tail != nullptr && hist > 0) {
+    float keep[MT][8];
+#pragma unroll
+    for (int j = 0; j < MT; ++j)
+      if (j < hist) input(sp.q_len - hist + j, keep[j]);
+#pragma unroll
+    for (int j = 0; j < MT; ++j)
+      if (j < hist) store8<T>(tail + (int64_t)j * C + c, keep[j]);
+  }
+}
+
 // ------------------------------------------------------------------ q/k unit norm, query temperature, K/V scatter
 // qkv: [T, H*dim | G*dim | G*vdim] (row stride given). Per head: q <- q / rms(q) * temp(pos), k <- k / rms(k),
 // temp(p) = 1 + coef * ln(floor((p + 1) / every) + 1). q and k are rewritten in place; k and v are also
@@ -172,6 +313,55 @@ unitnorm_temp_cache_kernel(T* __restrict__ qkv, int64_t stride, const int64_t* _
     x[i] = v;
     if (dst != nullptr) dst[i] = v;
   }
+}
+
+// 16-byte form: dim = 8 * GL with GL a power of two; GL adjacent lanes share one head, 32 / GL heads per warp
+template <typename T, int GL>
+__global__ void __launch_bounds__(256)
+unitnorm_temp_cache_vec_kernel(T* __restrict__ qkv, int64_t stride, const int64_t* __restrict__ positions,
+                               float eps, float coef, int every, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                               const int* __restrict__ slots, int slot_pairs, int block_size, int num_tokens,
+                               int H, int G, int vdim) {
+  pdl_wait();
+  constexpr int dim = GL * 8, UPW = 32 / GL;
+  const int lane = threadIdx.x & 31, gl = lane % GL;
+  const int64_t unit = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * UPW + lane / GL;
+  const int per_tok = H + 2 * G;
+  const bool live = unit < (int64_t)num_tokens * per_tok;
+  const int t = live ? (int)(unit / per_tok) : 0, u = live ? (int)(unit % per_tok) : 0;
+  int64_t slot = -1;
+  if (live && k_cache != nullptr && u >= H)
+    slot = slot_pairs ? (int64_t)slots[2 * t] * block_size + slots[2 * t + 1] : (int64_t)slots[t];
+  T* row = qkv + (int64_t)t * stride;
+  const bool is_v = u >= H + G;
+  if (live && is_v && slot >= 0) {
+    const T* src = row + (int64_t)(H + G) * dim + (int64_t)(u - H - G) * vdim;
+    T* dst = v_cache + slot * ((int64_t)G * vdim) + (int64_t)(u - H - G) * vdim;
+    for (int vi = gl; vi * 8 < vdim; vi += GL) {
+      float tmp[8];
+      load8<T>(src + vi * 8, tmp);
+      store8<T>(dst + vi * 8, tmp);
+    }
+  }
+  const bool normed = live && !is_v;
+  T* x = row + (int64_t)u * dim + gl * 8;
+  float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (normed) load8<T>(x, f);
+  float ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) ss += f[e] * f[e];
+#pragma unroll
+  for (int off = GL / 2; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  if (!normed) return;
+  float mul = 1.0f / sqrtf(ss / (float)dim + eps);
+  if (u < H) {
+    const int64_t steps = (positions[t] + 1) / every;
+    mul *= 1.0f + coef * logf((float)steps + 1.0f);
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) f[e] *= mul;
+  store8<T>(x, f);
+  if (u >= H && slot >= 0) store8<T>(k_cache + slot * ((int64_t)G * dim) + (int64_t)(u - H) * dim + gl * 8, f);
 }
 
 // ------------------------------------------------------------------ gated (grouped) RMS norm
@@ -230,6 +420,77 @@ act_and_mul_kernel(T* __restrict__ out, const T* __restrict__ x, int64_t rows, i
   }
 }
 
+template <typename T>
+__global__ void __launch_bounds__(256)
+act_and_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ x, int64_t rows, int inter8, int act) {
+  pdl_wait();
+  const int64_t total = rows * inter8;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / inter8;
+    const int c = (int)(i - r * inter8);
+    float g[8], u[8], o[8];
+    load8<T>(x + (r * 2 * inter8 + c) * 8, g);
+    load8<T>(x + (r * 2 * inter8 + inter8 + c) * 8, u);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float a = act == 1 ? fmaxf(g[e], 0.f) : act == 2 ? gelu_tanh_f(g[e]) : silu_f(g[e]);
+      o[e] = a * u[e];
+    }
+    store8<T>(out + i * 8, o);
+  }
+}
+
+// 16-byte form of gated_norm (n / groups % 8 == 0): one CTA per (row, group), 8 elements per thread and step
+template <typename T, typename Y>
+__global__ void __launch_bounds__(256)
+gated_norm_vec_kernel(T* __restrict__ out, const Y* __restrict__ y, const T* __restrict__ gate,
+                      int64_t gate_stride, const float* __restrict__ w, float eps, int n, int groups,
+                      int gate_first, int gate_act) {
+  __shared__ float red[32];
+  pdl_wait();
+  const int64_t r = blockIdx.x;
+  const int len = n / groups, lo = blockIdx.y * len;
+  const Y* yr = y + r * n + lo;
+  const T* gr = gate + r * gate_stride + lo;
+  T* o = out + r * n + lo;
+  constexpr int kV = 2;                               // up to 256 * 2 * 8 = 4096 elements per group in registers
+  float val[kV][8], gv[kV][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int m = 0; m < kV; ++m) {
+    const int vi = threadIdx.x + m * blockDim.x;
+    if (vi * 8 < len) {
+      load8<Y>(yr + vi * 8, val[m]);
+      load8<T>(gr + vi * 8, gv[m]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        gv[m][e] = gate_act == 1 ? silu_f(gv[m][e]) : sigmoid_f(gv[m][e]);
+        if (gate_first || w == nullptr) val[m][e] *= gv[m][e];
+        ss += val[m][e] * val[m][e];
+      }
+    }
+  }
+  float rstd = 1.f;
+  if (w != nullptr) rstd = 1.0f / sqrtf(cta_sum(ss, red) / (float)len + eps);
+#pragma unroll
+  for (int m = 0; m < kV; ++m) {
+    const int vi = threadIdx.x + m * blockDim.x;
+    if (vi * 8 < len) {
+      float ov[8];
+      if (w != nullptr) {
+        float wv[8];
+        load8<float>(w + lo + vi * 8, wv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ov[e] = gate_first ? val[m][e] * rstd * wv[e] : val[m][e] * rstd * wv[e] * gv[m][e];
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ov[e] = val[m][e];
+      }
+      store8<T>(o + vi * 8, ov);
+    }
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -253,6 +514,14 @@ extern "C" int b200_residual_add_norms(void* h, float* residual, const void* y, 
   B200_RETURN_IF(!residual || !y || !w_post || (w_pre && !h), B200_ERR_NULL_POINTER);
   const size_t smem = (size_t)hidden * sizeof(float);
   B200_RETURN_IF(smem > 200 * 1024, B200_ERR_UNSUPPORTED);
+  if (hidden % 8 == 0 && hidden <= 8 * 256 * kResVecs && aligned16(residual) && aligned16(y) && aligned16(w_post) &&
+      (!w_pre || (aligned16(w_pre) && aligned16(h)))) {
+    const int threads = hidden / 8 >= 256 ? 256 : ((hidden / 8 + 31) / 32) * 32;
+    B200_DISPATCH_3(dtype, T, launch_pdl(residual_add_norms_vec_kernel<T>, dim3(rows), dim3(threads), 0,
+                                         (cudaStream_t)stream, (T*)h, residual, (const T*)y, w_post, w_pre, offset,
+                                         eps, hidden));
+    return finish_launch();
+  }
   B200_DISPATCH_3(dtype, T, {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(residual_add_norms_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -273,6 +542,14 @@ extern "C" int b200_causal_conv(void* out, int64_t out_stride, const void* x, in
   B200_RETURN_IF(!out || !x || !weight || (cu_q == nullptr) == (ctx_lens == nullptr) || (cu_q && !cu_k) ||
                      (state && !state_slots), B200_ERR_NULL_POINTER);
   B200_RETURN_IF(out == x, B200_ERR_UNSUPPORTED);
+  if (channels % 8 == 0 && out_stride % 8 == 0 && x_stride % 8 == 0 && aligned16(out) && aligned16(x) &&
+      (!state || aligned16(state)) && taps <= 4) {
+    const dim3 vgrid((channels / 8 + 127) / 128, (max_q + kConvSeg - 1) / kConvSeg, num_seqs);
+    B200_DISPATCH_3(dtype, T, launch_pdl(causal_conv_vec_kernel<T, 4>, vgrid, dim3(128), 0, (cudaStream_t)stream,
+                                         (T*)out, out_stride, (const T*)x, x_stride, weight, bias, act, (T*)state,
+                                         state_slots, cu_q, cu_k, ctx_lens, channels, taps));
+    return finish_launch();
+  }
   const dim3 grid((channels + 127) / 128, (max_q + kConvSeg - 1) / kConvSeg, num_seqs);
   B200_DISPATCH_3(dtype, T, launch_pdl(causal_conv_kernel<T>, grid, dim3(128), 0, (cudaStream_t)stream, (T*)out,
                                        out_stride, (const T*)x, x_stride, weight, bias, act, (T*)state,
@@ -291,6 +568,27 @@ extern "C" int b200_unitnorm_temp_cache(void* qkv, int64_t stride, const int64_t
   B200_RETURN_IF(!qkv || !positions || (k_cache == nullptr) != (v_cache == nullptr) || (k_cache && !slots),
                  B200_ERR_NULL_POINTER);
   const int64_t units = (int64_t)num_tokens * (num_heads + 2 * num_kv_heads);
+  const int gl = dim / 8;
+  if (dim % 8 == 0 && (gl & (gl - 1)) == 0 && gl <= 32 && vdim % 8 == 0 && stride % 8 == 0 && aligned16(qkv) &&
+      (!k_cache || (aligned16(k_cache) && aligned16(v_cache)))) {
+    const int upw = 32 / gl;
+    const dim3 vgrid((unsigned)((units + 8 * upw - 1) / (8 * upw)));
+#define B200_UNITNORM_VEC(GLV)                                                                                       \
+  B200_DISPATCH_3(dtype, T, launch_pdl(unitnorm_temp_cache_vec_kernel<T, GLV>, vgrid, dim3(256), 0,                  \
+                                       (cudaStream_t)stream, (T*)qkv, stride, positions, eps, coef, every,          \
+                                       (T*)k_cache, (T*)v_cache, slots, slot_pairs, block_size, num_tokens,         \
+                                       num_heads, num_kv_heads, vdim))
+    switch (gl) {
+      case 1: B200_UNITNORM_VEC(1); break;
+      case 2: B200_UNITNORM_VEC(2); break;
+      case 4: B200_UNITNORM_VEC(4); break;
+      case 8: B200_UNITNORM_VEC(8); break;
+      case 16: B200_UNITNORM_VEC(16); break;
+      default: B200_UNITNORM_VEC(32); break;
+    }
+#undef B200_UNITNORM_VEC
+    return finish_launch();
+  }
   const dim3 grid((unsigned)((units + 7) / 8));
   B200_DISPATCH_3(dtype, T, launch_pdl(unitnorm_temp_cache_kernel<T>, grid, dim3(256), 0, (cudaStream_t)stream,
                                        (T*)qkv, stride, positions, eps, coef, every, (T*)k_cache, (T*)v_cache,
@@ -308,6 +606,20 @@ extern "C" int b200_gated_norm(void* out, const void* y, int32_t y_is_f32, const
   B200_RETURN_IF(!out || !y || !gate, B200_ERR_NULL_POINTER);
   const dim3 grid(rows, weight ? groups : 1);
   const int g = weight ? groups : 1;
+  const int len = n / g;
+  if (len % 8 == 0 && len <= 4096 && n % 8 == 0 && gate_stride % 8 == 0 && aligned16(out) && aligned16(y) &&
+      aligned16(gate) && (!weight || aligned16(weight))) {
+    const int threads = len / 8 >= 256 ? 256 : ((len / 8 + 31) / 32) * 32;
+    B200_DISPATCH_3(dtype, T, {
+      if (y_is_f32)
+        launch_pdl(gated_norm_vec_kernel<T, float>, grid, dim3(threads), 0, (cudaStream_t)stream, (T*)out,
+                   (const float*)y, (const T*)gate, gate_stride, weight, eps, n, g, gate_first, gate_act);
+      else
+        launch_pdl(gated_norm_vec_kernel<T, T>, grid, dim3(threads), 0, (cudaStream_t)stream, (T*)out, (const T*)y,
+                   (const T*)gate, gate_stride, weight, eps, n, g, gate_first, gate_act);
+    });
+    return finish_launch();
+  }
   B200_DISPATCH_3(dtype, T, {
     if (y_is_f32)
       launch_pdl(gated_norm_kernel<T, float>, grid, dim3(256), 0, (cudaStream_t)stream, (T*)out,
@@ -324,6 +636,14 @@ extern "C" int b200_act_and_mul(void* out, const void* x, int32_t rows, int32_t 
   B200_RETURN_IF(rows < 0 || inter <= 0 || act < 0 || act > 2, B200_ERR_BAD_SHAPE);
   if (rows == 0) return B200_OK;
   B200_RETURN_IF(!out || !x, B200_ERR_NULL_POINTER);
+  if (inter % 8 == 0 && aligned16(out) && aligned16(x)) {
+    const int64_t vecs = (int64_t)rows * (inter / 8);
+    int vgrid = (int)((vecs + 255) / 256);
+    if (vgrid > 148 * 16) vgrid = 148 * 16;
+    B200_DISPATCH_3(dtype, T, launch_pdl(act_and_mul_vec_kernel<T>, dim3(vgrid), dim3(256), 0, (cudaStream_t)stream,
+                                         (T*)out, (const T*)x, (int64_t)rows, inter / 8, act));
+    return finish_launch();
+  }
   const int64_t total = (int64_t)rows * inter;
   int grid = (int)((total + 255) / 256);
   if (grid > 148 * 16) grid = 148 * 16;
