@@ -726,6 +726,9 @@ def hybrid_compare(args):
         for name in pair.split(":"):
             llm = LLM(name, kvcache_block_size=args.block_size, max_num_seqs=B, max_model_len=max(4096, ctx + W + K + 16),
                       max_num_batched_tokens=16384, gpu_memory_utilization=args.mem_util, seed=0)
+            decode_workload(llm, Group(1), B, ctx, 4, 3, 1, 0)      # untimed: first-call set-up of every kernel
+            while not llm.is_finished():
+                llm.step()
             r = decode_workload(llm, Group(1), B, ctx, K, W, 0, 0)
             n_params = sum(p.numel() for p in llm.model_runner.model.parameters())
             out["models"].append({"model": name, "parameters_M": round(n_params / 1e6),

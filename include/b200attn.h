@@ -426,7 +426,7 @@ int b200_residual_add_norms(void* h, float* residual, const void* y, const float
 
 /* Depth-wise causal convolution over time: out[t, c] = act(bias[c] + sum_j w[c, j] x[t - taps + 1 + j, c]),
  * zeros before a sequence's start; state [slots, taps - 1, channels] (dtype) carries each sequence's last
- * taps - 1 inputs between steps. act: 0 none, 1 silu. taps <= 8. out must not alias x. */
+ * taps - 1 inputs between steps. act: 0 none, 1 silu. taps <= 16. out must not alias x. */
 int b200_causal_conv(void* out, int64_t out_stride, const void* x, int64_t x_stride, const float* weight,
                      const float* bias, int32_t act, void* state, const int32_t* state_slots,
                      const int32_t* cu_q, const int32_t* cu_k, const int32_t* ctx_lens, int32_t num_seqs,

@@ -127,7 +127,7 @@ residual_add_norms_vec_kernel(T* __restrict__ h, float* __restrict__ res, const 
 // first segment reads the carried tail, and the same thread writes the new one (from the chunk's last rows,
 // which it reads itself), so no other thread can see a half-updated tail.
 constexpr int kConvSeg = 16;
-constexpr int kConvMaxTaps = 8;
+constexpr int kConvMaxTaps = 16;
 
 template <typename T>
 __global__ void __launch_bounds__(128)
