@@ -120,6 +120,11 @@ class LLMEngine:
         portions beside single tokens; a request is admitted at its first entry and gives back its blocks
         and state slot when it is named in ``end``. Nothing is sampled. Returns fp32 logits
         [wanted places in entry order, vocab] on the host, or None. Needs ``return_logits=True``."""
+        entries = [e for e in entries if e[1]]
+        if not entries:
+            for request_id in end:
+                self.scheduler.finish_given(request_id)
+            return None
         seqs, is_prefill = self.scheduler.schedule_given([(rid, tokens) for rid, tokens, _ in entries])
         rows, base = [], 0
         for i, (_, tokens, want) in enumerate(entries):
