@@ -22,6 +22,8 @@ context tensor-parallel over all N GPUs (fused NVLink all-reduce + residual add 
 the all-reduce form and its latency, and the same workload at TP=1 (rank 0) for the speed-up.
 `--tp` instead makes the tensor-parallel engine the whole line ("strong" scaling).
 `--impl reference` times only the CPU reference arm.
+`--hybrid` leaves the contract workload aside: the Zegopel hybrid decoder beside the dense decoder of the same width
+(prefill and decode throughput through the engine) and the rooflines of its kernels beside their like kernels.
 """
 from __future__ import annotations
 
@@ -786,7 +788,8 @@ def main():
     r = decode_workload(llm, group, B, ctx, K, W, rank if not args.tp else 0, rank)
     peak, peak_src = peaks()
     fp8 = args.kv_cache_dtype != "auto"
-    roof = attention_roofline(runner, group, B, K, world if args.tp else 1, fp8, peak, peak_src)
+    hybrid = runner.kv_cache.dim() != 5      # per-layer caches of a hybrid decoder: no single KV stream to time alone
+    roof = None if hybrid else attention_roofline(runner, group, B, K, world if args.tp else 1, fp8, peak, peak_src)
     dbg(rank, 'attn loop done')
     clk = clocks.stop()
 
@@ -795,9 +798,12 @@ def main():
     engines = 1 if args.tp else world
     value = engines * B * K / dev_s
     # KV-read roofline of the whole step at the measured peak (what `value` is bounded by)
-    step_kv_bytes = roof["algorithmic_bytes_per_launch"] * roof["layers"] * roof["launches_per_layer"]
-    roof["step_kv_roofline_tokens_per_s"] = B / (step_kv_bytes / (peak * 1e9))
-    roof["step_frac_of_kv_roofline"] = (B * K / dev_s) / roof["step_kv_roofline_tokens_per_s"]
+    if roof is None:
+        roof = {"note": "hybrid decoder: see `bench.py --hybrid` for its kernels' rooflines"}
+    else:
+        step_kv_bytes = roof["algorithmic_bytes_per_launch"] * roof["layers"] * roof["launches_per_layer"]
+        roof["step_kv_roofline_tokens_per_s"] = B / (step_kv_bytes / (peak * 1e9))
+        roof["step_frac_of_kv_roofline"] = (B * K / dev_s) / roof["step_kv_roofline_tokens_per_s"]
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
         "ms_per_step": dev_s / K * 1e3, "higher_is_better": True, "scaling": "weak" if not args.tp else "strong",
