@@ -28,6 +28,7 @@ from .. import ops
 from ..layers.embed_head import ParallelLMHead, VocabParallelEmbedding
 from ..layers.linear import MergedColumnParallelLinear, ReplicatedLinear, RowParallelLinear, tp_rank_size
 from ..layers.seq_mixers import (GatedNorm, LinearRecurrence, ShortConv, VarSizeAttention, small_param)
+from ..utils.context import get_context
 
 NORM_OFFSET = 1.0          # norm weights of the residual path are stored as deviations from one
 FF_ACT = "relu"
@@ -67,12 +68,10 @@ class AttentionMixer(nn.Module):
         self.o_proj = RowParallelLinear(H * dv, width)
 
     def forward(self, positions, h):
-        ctx_tokens = h.shape[0]
         qkvg = self.proj(h)
         nq, nk, nv = self.sizes[:3]
         qkv = self.conv(qkvg[:, :nq + nk + nv])
         attn = self.attn
-        from ..utils.context import get_context
         ctx = get_context()
         have_cache = attn.k_cache.numel() > 0 and ctx.slot_mapping is not None
         ops.unitnorm_temp_cache(qkv, positions, self.eps, self.temp_coef, self.temp_every, self.H, self.G, self.d,
@@ -82,7 +81,6 @@ class AttentionMixer(nn.Module):
         k = qkv[:, nq:nq + nk].unflatten(1, (self.G, self.d))
         v = qkv[:, nq + nk:].unflatten(1, (self.G, self.dv))
         o = attn(q, k, v)
-        assert o.shape[0] == ctx_tokens
         return self.o_proj(self.gate(o, qkvg[:, nq + nk + nv:]))
 
 

@@ -8,7 +8,6 @@ The schedules are fed through LLMEngine.step_given -- the scheduler's block mana
 model's kernels -- so what is compared is the engine, not a forward function.
 """
 import json
-import math
 import os
 import random
 
