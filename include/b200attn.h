@@ -464,11 +464,15 @@ int b200_attn_generic(void* out, const void* q, int64_t q_stride, const void* k,
 /* Per head S_t = a_t S_(t-1) + k_t (b_t v_t)^T, o_t = S_t^T q_t; S fp32 [kdim, vdim] in state
  * [slots, H, kdim, vdim]. q, k [T, groups*kdim] (head h reads group h / (H / groups)), v [T, H*vdim];
  * out fp32 [T, H*vdim]. mode 0: a_t = decay[h], b_t = 1, optional silu on q, k, v as read. mode 1:
- * step = softplus(dt[t, h] + dt_bias[h]), a_t = exp(-exp(a_log[h]) step), b_t = step, o_t += d_skip[h] v_t. */
+ * step = softplus(dt[t, h] + dt_bias[h]), a_t = exp(-exp(a_log[h]) step), b_t = step, o_t += d_skip[h] v_t.
+ * max_q: the longest span of the step; bf16 prompt portions (max_q >= 16, kdim, vdim <= 128) run 16 tokens
+ * at a time on the tensor cores with every fp32 operand split into three bf16 terms, everything else token
+ * by token on the fp32 pipes. */
 int b200_linear_recurrence(float* out, const void* q, int64_t q_stride, const void* k, int64_t k_stride,
                            const void* v, int64_t v_stride, float* state, const int32_t* state_slots,
                            const int32_t* cu_q, const int32_t* cu_k, const int32_t* ctx_lens,
-                           int32_t num_seqs, int32_t num_heads, int32_t groups, int32_t kdim, int32_t vdim,
+                           int32_t num_seqs, int32_t max_q, int32_t num_heads, int32_t groups, int32_t kdim,
+                           int32_t vdim,
                            int32_t mode, int32_t act_silu, const float* decay, const void* dt,
                            int64_t dt_stride, const float* dt_bias, const float* a_log, const float* d_skip,
                            int32_t dtype, b200_stream_t stream);

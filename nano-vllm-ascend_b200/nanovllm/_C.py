@@ -116,7 +116,7 @@ PROTOTYPES = {
                                     c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,
                                     c_int32, c_int32, c_int32, c_float, c_int32, c_void_p]),
     "b200_linear_recurrence": (c_int32, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
-                                         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32,
+                                         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,
                                          c_int32, c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p,
                                          c_int64, c_void_p, c_void_p, c_void_p, c_int32, c_void_p]),
     "b200_sample": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int64, c_uint64,

@@ -766,7 +766,7 @@ def linear_recurrence(q, k, v, spans: StepSpans, num_heads, groups, kdim, vdim, 
     stride = lambda t: t.stride(0) if T > 1 else t.shape[1]
     _C.check(_C.load().b200_linear_recurrence(
         out.data_ptr(), q.data_ptr(), stride(q), k.data_ptr(), stride(k), v.data_ptr(), stride(v), _ptr(state),
-        _ptr(state_slots), cu_q, cu_k, ctx, spans.num_seqs, num_heads, groups, kdim, vdim, mode,
+        _ptr(state_slots), cu_q, cu_k, ctx, spans.num_seqs, spans.max_q, num_heads, groups, kdim, vdim, mode,
         1 if act_silu else 0, _ptr(decay), _ptr(dt), stride(dt) if dt is not None else 0, _ptr(dt_bias),
         _ptr(a_log), _ptr(d_skip), _dt3(q), _stream()), "b200_linear_recurrence")
     return out
