@@ -446,6 +446,60 @@ def test_selective_recurrence(H, G, N, dv):
         lo += n
 
 
+@pytest.mark.parametrize("H,G,N,dv,mode", [(2, 2, 128, 64, "selective"), (3, 1, 20, 12, "selective"),
+                                             (2, 2, 64, 128, "decay"), (4, 4, 24, 40, "decay")])
+def test_recurrence_sixteen_tokens_at_a_time(H, G, N, dv, mode):
+    """bf16 prompt portions run on the tensor cores, 16 tokens per step with every fp32 operand split into three
+    bf16 terms: the result must agree with the token-by-token recurrence to fp32 accuracy (the inputs are bf16
+    values, so the float64 oracle sees exactly the same numbers). Portions of 40, 17, 16 and 33 tokens cross the
+    16-token steps at every offset; a second sequence of one long portion shares the launches; then single tokens."""
+    from nanovllm import ops
+    g = torch.Generator().manual_seed(N + dv)
+    bf = torch.bfloat16
+    lens = [40 + 17 + 16 + 33 + 3, 90]
+    T = sum(lens)
+    q = (torch.randn(T, G, N, generator=g) * 0.3).to(bf)
+    k = (torch.randn(T, G, N, generator=g) * 0.3).to(bf)
+    v = torch.randn(T, H, dv, generator=g).to(bf)
+    state = torch.full((3, H, N, dv), 9.0).cuda()
+    slots = torch.tensor([2, 0], dtype=torch.int32).cuda()
+    if mode == "decay":
+        assert G == H
+        decay = torch.tensor([0.999, 0.9, 0.5, 0.97][:H])
+        kw = dict(decay=decay.cuda())
+    else:
+        dt = (torch.randn(T, H, generator=g)).to(bf)
+        dt_bias, A_log, D = torch.randn(H, generator=g), torch.rand(H, generator=g) * 2 - 2, torch.randn(H, generator=g)
+        kw = dict(dt_bias=dt_bias.cuda(), a_log=A_log.cuda(), d_skip=D.cuda())
+    full = torch.zeros(T, H * dv)
+    at = [0, 0]
+    for portion in ([40, 90], [17, 0], [16, 0], [33, 0], [1, 0], [1, 0], [1, 0]):
+        idx = torch.cat([torch.arange(at[0], at[0] + portion[0]), lens[0] + torch.arange(at[1], at[1] + portion[1])])
+        qs = [p for p in portion if p]
+        ks = [a + p for a, p in zip(at, portion) if p]
+        if qs == [1]:
+            sp = ops.StepSpans(None, None, torch.tensor(ks, dtype=torch.int32).cuda())
+        else:
+            sp = _spans(qs, ks)
+        extra = dict(kw, dt=dt[idx].cuda()) if mode == "selective" else kw
+        out = ops.linear_recurrence(q[idx].reshape(len(idx), -1).cuda(), k[idx].reshape(len(idx), -1).cuda(),
+                                    v[idx].reshape(len(idx), -1).cuda(), sp, H, G, N, dv, state, slots[:len(qs)],
+                                    **extra).cpu()
+        full[idx] = out
+        at = [a + p for a, p in zip(at, portion)]
+    assert at == lens
+    lo = 0
+    for n in lens:
+        sl = slice(lo, lo + n)
+        if mode == "decay":
+            want = O.decay_recurrence(q[sl].to(F64), k[sl].to(F64), v[sl].to(F64), decay.to(F64))
+        else:
+            step = torch.nn.functional.softplus(dt[sl].to(F64) + dt_bias.to(F64), threshold=1e9)
+            want = O.selective_scan(v[sl].to(F64), k[sl].to(F64), q[sl].to(F64), step, A_log.to(F64), D.to(F64))
+        assert (full[sl].to(F64) - want.reshape(n, -1)).abs().max() < 1e-4 * want.abs().max(), (mode, lo)
+        lo += n
+
+
 def test_gated_norms_and_feed_forward_activation():
     from nanovllm import ops
     g = torch.Generator().manual_seed(4)
