@@ -53,7 +53,7 @@ class ModelCfg:
 
     @staticmethod
     def llama_3_2_1b():
-        # rope_theta: the model card's 500000. (Under transformers>=5 the reference's
+        # rope_theta: the published configuration's 500000. (Under transformers>=5 the reference's
         # getattr(config, "rope_theta", 10000) at llama.py:133 falls back to 10000; the base is
         # an input of this oracle, parity tests pass the same value to both sides.)
         return ModelCfg(vocab_size=128256, hidden_size=2048, num_layers=16, num_heads=32,

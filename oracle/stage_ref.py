@@ -1,7 +1,7 @@
 """Pack the reference modules of the hot path into oracle/_ref/reference_path.zip (git-ignored; NOT
 gpurun-ignored, so the archive travels to the GPU box with the snapshot like a built .so does).
 
-Why: the reference is pure Python, there is nothing to compile -- "building" it for the checker
+Why: the reference is pure Python, there is nothing to compile -- "building" it for the oracle
 means making the unmodified modules importable where /root/reference does not exist. With the
 archive present `bench.py --impl reference` and the `cpu_baseline` leg run the reference's own
 models/qwen3.py + layers/attention_torch_native.py (cpu_baseline.kind = "reference"); without it
