@@ -452,14 +452,16 @@ int b200_gated_norm(void* out, const void* y, int32_t y_is_f32, const void* gate
 int b200_act_and_mul(void* out, const void* x, int32_t rows, int32_t inter, int32_t act, int32_t dtype,
                      b200_stream_t stream);
 
-/* Causal softmax attention for any key size `dim` and value size `vdim` (<= 256), packed keys
+/* Causal softmax attention for any key size `dim` and value size `vdim` (<= 512), packed keys
  * (block_tables == NULL: k, v are this step's rows in the order of cu_k) or paged caches
- * [nb, bs, G*dim] / [nb, bs, G*vdim]. q [T, H, dim] -> out [T, H*vdim]. fp32 scores and accumulation. */
+ * [nb, bs, G*dim] / [nb, bs, G*vdim]. q [T, H, dim] -> out [T, H*vdim]. fp32 scores and accumulation.
+ * window > 0: the query at position i sees keys j with 0 <= i - j < window. v == NULL: the values are the
+ * first vdim columns of the key rows (one cached latent row serves as key and as value; vdim <= dim). */
 int b200_attn_generic(void* out, const void* q, int64_t q_stride, const void* k, int64_t k_stride,
                       const void* v, int64_t v_stride, const int32_t* block_tables, int32_t bt_stride,
                       int32_t block_size, const int32_t* cu_q, const int32_t* cu_k, const int32_t* ctx_lens,
                       int32_t num_seqs, int32_t max_q, int32_t num_heads, int32_t num_kv_heads, int32_t dim,
-                      int32_t vdim, float scale, int32_t dtype, b200_stream_t stream);
+                      int32_t vdim, float scale, int32_t window, int32_t dtype, b200_stream_t stream);
 
 /* Per head S_t = a_t S_(t-1) + k_t (b_t v_t)^T, o_t = S_t^T q_t; S fp32 [kdim, vdim] in state
  * [slots, H, kdim, vdim]. q, k [T, groups*kdim] (head h reads group h / (H / groups)), v [T, H*vdim];
@@ -467,7 +469,8 @@ int b200_attn_generic(void* out, const void* q, int64_t q_stride, const void* k,
  * step = softplus(dt[t, h] + dt_bias[h]), a_t = exp(-exp(a_log[h]) step), b_t = step, o_t += d_skip[h] v_t.
  * max_q: the longest span of the step; bf16 prompt portions (max_q >= 16, kdim, vdim <= 128) run 16 tokens
  * at a time on the tensor cores with every fp32 operand split into three bf16 terms, everything else token
- * by token on the fp32 pipes. */
+ * by token on the fp32 pipes. qk_f32: q and k are fp32 whatever the dtype (rotated or normalised upstream in
+ * 32-bit; mode 0 only, token by token), v stays in dtype. */
 int b200_linear_recurrence(float* out, const void* q, int64_t q_stride, const void* k, int64_t k_stride,
                            const void* v, int64_t v_stride, float* state, const int32_t* state_slots,
                            const int32_t* cu_q, const int32_t* cu_k, const int32_t* ctx_lens,
@@ -475,7 +478,81 @@ int b200_linear_recurrence(float* out, const void* q, int64_t q_stride, const vo
                            int32_t vdim,
                            int32_t mode, int32_t act_silu, const float* decay, const void* dt,
                            int64_t dt_stride, const float* dt_bias, const float* a_log, const float* d_skip,
-                           int32_t dtype, b200_stream_t stream);
+                           int32_t qk_f32, int32_t dtype, b200_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------
+ * Multi-stream residuals, rotary positions, delta rule, latent attention, clamped gated unit
+ * (csrc/stream_ops.cu, csrc/delta_rule.cu) and the generic mixture-of-experts kernels (csrc/moe_generic.cu).
+ * dtype: BF16, F16 or F32. */
+
+/* x [rows, streams, hidden] fp32, in place: with y (dtype, [rows, hidden]) every stream t becomes
+ * sum_s mix[s][t] x_s + out_w[t] y; then u = sum_t in_w[t] x_t (in_w == NULL: plain sum) and, when w is
+ * given, h = norm(u) in dtype: kind 0 layer norm (u - mean) / sqrt(var + eps) * w + b, kind 1 RMS norm
+ * u / sqrt(mean u^2 + eps) * (offset + w). sum_out (optional, fp32 [rows, hidden]) receives u. streams <= 8. */
+int b200_stream_mix_norm(void* h, float* x, const void* y, const float* mix, const float* out_w,
+                         const float* in_w, const float* w, const float* b, float* sum_out, float eps,
+                         float offset, int32_t kind, int32_t rows, int32_t streams, int32_t hidden,
+                         int32_t dtype, b200_stream_t stream);
+
+/* Rotary positions on `heads` heads of `width` columns per token: the first `dims` columns are rotated by the
+ * angle pos * base^(-2i/dims) in pairs (2i, 2i+1) (interleaved) or (i, i + dims/2), the rest pass; heads below
+ * `split` are multiplied by scale_lo, the others by scale_hi (after the rotation). Head hd of token t is read at
+ * in + t * in_stride + hd * in_head and written at out + t * out_stride + hd * out_head, as fp32 (out_f32) or
+ * dtype. Angles are computed in fp64. */
+int b200_rotary_heads(void* out, int64_t out_stride, int32_t out_head, int32_t out_f32, const void* in,
+                      int64_t in_stride, int32_t in_head, const int64_t* positions, int32_t tokens,
+                      int32_t heads, int32_t width, int32_t dims, double base, int32_t interleaved,
+                      int32_t split, float scale_lo, float scale_hi, int32_t dtype, b200_stream_t stream);
+
+/* Inputs of b200_delta_rule from projected activations: qk [T, 2*groups*dim] fp32 = q and k heads of qk_in
+ * divided by sqrt(sum x^2 + unit_eps), q also times q_scale; decay [T, H*dim] fp32 =
+ * exp(-exp(a_log[h]) softplus(a[t, h*dim + i] + dt_bias[h*dim + i])); beta [T, H] = sigmoid(b[t, h]). */
+int b200_delta_prep(float* qk, float* decay, float* beta, const void* qk_in, int64_t qk_stride, const void* a,
+                    int64_t a_stride, const void* b, int64_t b_stride, const float* dt_bias, const float* a_log,
+                    int32_t tokens, int32_t num_heads, int32_t groups, int32_t dim, float unit_eps,
+                    float q_scale, int32_t dtype, b200_stream_t stream);
+
+/* Gated delta rule per head: S <- diag(g_t) S; w = beta_t (v_t - S^T k_t); S <- S + k_t w^T; o_t = S^T q_t,
+ * S fp32 [kdim, vdim] in state [slots, H, kdim, vdim]. q, k fp32 [T, groups*kdim] (row strides given),
+ * g fp32 [T, H*kdim], beta fp32 [T, H], v [T, H*vdim] in dtype; out fp32 [T, H*vdim]. kdim <= 256. */
+int b200_delta_rule(float* out, const float* q, int64_t q_stride, const float* k, int64_t k_stride,
+                    const void* v, int64_t v_stride, const float* g, const float* beta, float* state,
+                    const int32_t* state_slots, const int32_t* cu_q, const int32_t* cu_k,
+                    const int32_t* ctx_lens, int32_t num_seqs, int32_t num_heads, int32_t groups, int32_t kdim,
+                    int32_t vdim, int32_t dtype, b200_stream_t stream);
+
+/* Latent attention, per token: cq [T, q_rank] = rms(dq) * wq; row = [rms(dkv[:rank]) * wc | rotary(dkv[rank:])]
+ * (rot columns, the first `dims` rotated) written to kc [T, rank + rot] (optional) and to the paged cache
+ * [nb, bs, rank + rot] at `slots` (flat, or (block, offset) pairs; optional). */
+int b200_latent_kv_prep(void* cq, void* kc, void* cache, const int32_t* slots, int32_t slot_pairs,
+                        int32_t block_size, const void* dq, int64_t dq_stride, const void* dkv,
+                        int64_t dkv_stride, const float* wq, const float* wc, const int64_t* positions,
+                        int32_t tokens, int32_t q_rank, int32_t rank, int32_t rot, int32_t dims, double base,
+                        int32_t interleaved, float eps, int32_t dtype, b200_stream_t stream);
+
+/* out[r, i] = g sigmoid(alpha g) (u + 1), g = min(x[r, i], limit), u = clamp(x[r, inter + i], -limit, limit). */
+int b200_glu_clamped(void* out, const void* x, int32_t rows, int32_t inter, float alpha, float limit,
+                     int32_t dtype, b200_stream_t stream);
+
+/* Router: s = sigmoid(logits) (fp32 [T, E]); choice = s + bias; experts form `groups` equal groups of
+ * neighbours, a group scores the sum of its two largest choices and only the `keep` best groups stay in play;
+ * the top_k choices are taken (ties to the lower index); weights = s / (sum s + 1e-20) * scale, fp32. */
+int b200_moe_route_grouped(int32_t* topk_ids, float* topk_weights, const float* router_logits,
+                           int64_t logit_stride, const float* bias, int32_t tokens, int32_t num_experts,
+                           int32_t top_k, int32_t groups, int32_t keep, float scale, b200_stream_t stream);
+
+/* Expert GEMMs for any sizes and dtypes over the plan of b200_moe_align. gate_up: out [pairs, n_out] (dtype) =
+ * silu(x Wg^T) * (x Wu^T), x rows gathered by sorted_pair / top_k, w [E, 2*n_out, K]. Otherwise: out
+ * [pairs, n_out] fp32 = a W^T with a [pairs, K] in plan order, w [E, n_out, K]. */
+int b200_moe_gemm_generic(void* out, const void* a, int64_t a_stride, const void* w, const int32_t* offsets,
+                          const int32_t* sorted_pair, int32_t num_pairs, int32_t K, int32_t n_out,
+                          int32_t num_local, int32_t top_k, int32_t gate_up, int32_t dtype,
+                          b200_stream_t stream);
+
+/* out[t] = sum_j topk_weights[t, j] y[pos_of_pair[t, j]] (fp32 accumulation, pairs with pos < 0 skipped). */
+int b200_moe_combine_weighted(void* out, const float* y, const float* topk_weights, const int32_t* pos_of_pair,
+                              int32_t tokens, int32_t top_k, int32_t hidden, int32_t dtype,
+                              b200_stream_t stream);
 
 #ifdef __cplusplus
 }

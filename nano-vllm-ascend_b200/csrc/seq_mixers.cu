@@ -17,7 +17,7 @@ namespace b200 {
 // time in shared memory as fp32; lane j scores key j, then each lane owns value channels lane, lane+32, ...
 constexpr int kAttnRows = 8;
 constexpr int kAttnKeys = 32;
-constexpr int kAttnMaxVChunks = 8;     // value size <= 256
+constexpr int kAttnMaxVChunks = 16;    // value size <= 512
 
 template <typename T>
 __global__ void __launch_bounds__(kAttnRows * 32)
@@ -25,7 +25,7 @@ attn_generic_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_stri
                     int64_t k_stride, const T* __restrict__ v, int64_t v_stride,
                     const int* __restrict__ block_tables, int bt_stride, int block_size,
                     const int* __restrict__ cu_q, const int* __restrict__ cu_k, const int* __restrict__ ctx_lens,
-                    int H, int G, int dim, int vdim, float scale) {
+                    int H, int G, int dim, int vdim, float scale, int window) {
   extern __shared__ float smem[];
   pdl_wait();
   const int s = blockIdx.z, g = blockIdx.y;
@@ -38,12 +38,16 @@ attn_generic_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_stri
   const int kpad = dim + 1;
   float* sq = smem;                                   // [8][dim]
   float* sk = sq + kAttnRows * dim;                   // [32][dim + 1]
-  float* sv = sk + kAttnKeys * kpad;                  // [32][vdim]
+  // v == nullptr: the values are the first vdim columns of the key rows (one latent row serves as key and value)
+  const bool v_in_k = v == nullptr;
+  float* sv = v_in_k ? sk : sk + kAttnKeys * kpad;    // [32][vdim]
+  const int vpad = v_in_k ? kpad : vdim;
 
   const int r = r0 + warp;
   const bool live = r < rows;
   const int tok = live ? r / rep : 0, head = g * rep + (live ? r % rep : 0);
-  const int pos = sp.first_pos() + tok;               // this row sees keys 0 .. pos
+  const int pos = sp.first_pos() + tok;               // this row sees keys lo .. pos
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
   if (live) {
     const T* qr = q + (int64_t)(sp.q_start + tok) * q_stride + (int64_t)head * dim;
     for (int i = lane; i < dim; i += 32) sq[warp * dim + i] = to_f32<T>(qr[i]);
@@ -56,7 +60,9 @@ attn_generic_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_stri
 #pragma unroll
   for (int c = 0; c < kAttnMaxVChunks; ++c) acc[c] = 0.f;
 
-  for (int j0 = 0; j0 <= max_pos; j0 += kAttnKeys) {
+  const int min_pos = sp.first_pos() + r0 / rep;
+  const int first_key = window > 0 ? max(0, min_pos - window + 1) : 0;
+  for (int j0 = first_key; j0 <= max_pos; j0 += kAttnKeys) {
     __syncthreads();                                  // previous tile fully consumed (and sq written)
     const int nk = min(kAttnKeys, max_pos + 1 - j0);
     for (int e = threadIdx.x; e < nk * dim; e += blockDim.x) {
@@ -67,7 +73,7 @@ attn_generic_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_stri
                               : k_base + key;
       sk[j * kpad + i] = to_f32<T>(k[row * k_stride + (int64_t)g * dim + i]);
     }
-    for (int e = threadIdx.x; e < nk * vdim; e += blockDim.x) {
+    for (int e = threadIdx.x; e < (v_in_k ? 0 : nk * vdim); e += blockDim.x) {
       const int j = e / vdim, i = e - j * vdim;
       const int key = j0 + j;
       const int64_t row = block_tables != nullptr
@@ -76,9 +82,9 @@ attn_generic_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_stri
       sv[j * vdim + i] = to_f32<T>(v[row * v_stride + (int64_t)g * vdim + i]);
     }
     __syncthreads();
-    if (!live || j0 > pos) continue;
+    if (!live || j0 > pos || j0 + nk <= lo) continue;
     float sc = -INFINITY;
-    if (lane < nk && j0 + lane <= pos) {
+    if (lane < nk && j0 + lane <= pos && j0 + lane >= lo) {
       float d = 0.f;
       const float* kr = sk + lane * kpad;
       const float* qr = sq + warp * dim;
@@ -97,7 +103,7 @@ attn_generic_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_stri
 #pragma unroll
       for (int c = 0; c < kAttnMaxVChunks; ++c) {
         const int i = lane + 32 * c;
-        if (i < vdim) acc[c] += pj * sv[j * vdim + i];
+        if (i < vdim) acc[c] += pj * sv[j * vpad + i];
       }
     }
   }
@@ -126,7 +132,7 @@ constexpr int kRecTok = 8;
 __device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
 struct RecParams {
-  const void *q, *k, *v;            // element type T; q, k: [tokens, groups * kdim]; v: [tokens, H * vdim]
+  const void *q, *k, *v;            // q, k: [tokens, groups * kdim] of type T; v: [tokens, H * vdim] of type TV
   int64_t q_stride, k_stride, v_stride;
   float* out;                       // [tokens, H * vdim] fp32
   float* state;                     // [slots, H, kdim, vdim] fp32 or nullptr (start from zero, keep nothing)
@@ -140,7 +146,7 @@ struct RecParams {
   const float *dt_bias, *a_log, *d_skip;   // mode 1: [H] each
 };
 
-template <typename T, int KPT, int NS>
+template <typename T, typename TV, int KPT, int NS>
 __global__ void __launch_bounds__(128)
 linear_recurrence_kernel(const RecParams P) {
   extern __shared__ __align__(16) float smem[];
@@ -179,7 +185,7 @@ linear_recurrence_kernel(const RecParams P) {
   }
   const T* q = (const T*)P.q + (int64_t)grp * kdim;
   const T* k = (const T*)P.k + (int64_t)grp * kdim;
-  const T* v = (const T*)P.v + (int64_t)h * vdim + c0;
+  const TV* v = (const TV*)P.v + (int64_t)h * vdim + c0;
   const T* dt = (const T*)P.dt;
   const float a_const = P.mode == 0 ? P.decay[h] : 0.f;
   const float rate = P.mode == 1 ? expf(P.a_log[h]) : 0.f;
@@ -189,7 +195,8 @@ linear_recurrence_kernel(const RecParams P) {
 
   constexpr int NQ = (kRecTok * KP + 127) / 128;     // q (and k) elements per thread per batch
   constexpr int NV = kRecTok * CC / 128;
-  T pq[NQ], pk[NQ], pv[NV], pdt = from_f32<T>(0.f);
+  T pq[NQ], pk[NQ], pdt = from_f32<T>(0.f);
+  TV pv[NV];
   auto fetch = [&](int t0) {
     const int nt = min(kRecTok, sp.q_len - t0);
     const int64_t tok0 = sp.q_start + t0;
@@ -206,7 +213,7 @@ linear_recurrence_kernel(const RecParams P) {
     for (int n = 0; n < NV; ++n) {
       const int e = threadIdx.x + n * 128;
       const int tt = e / CC, c = e % CC;
-      pv[n] = (tt < nt && c < vcols) ? v[(tok0 + tt) * P.v_stride + c] : from_f32<T>(0.f);
+      pv[n] = (tt < nt && c < vcols) ? v[(tok0 + tt) * P.v_stride + c] : from_f32<TV>(0.f);
     }
     if (P.mode == 1 && threadIdx.x < nt) pdt = dt[(tok0 + threadIdx.x) * P.dt_stride + h];
   };
@@ -231,8 +238,8 @@ linear_recurrence_kernel(const RecParams P) {
 #pragma unroll
     for (int n = 0; n < NV; ++n) {
       const int e = threadIdx.x + n * 128;
-      float x = to_f32<T>(pv[n]);
-      if (P.act_silu) x = to_f32<T>(from_f32<T>(sizeof(T) == 2 ? silu_fast(x) : silu_f(x)));
+      float x = to_f32<TV>(pv[n]);
+      if (P.act_silu) x = to_f32<TV>(from_f32<TV>(sizeof(TV) == 2 ? silu_fast(x) : silu_f(x)));
       sx[e] = x;
     }
     if (threadIdx.x < nt) {
@@ -290,12 +297,12 @@ linear_recurrence_kernel(const RecParams P) {
   }
 }
 
-template <typename T, int KPT, int NS>
+template <typename T, typename TV, int KPT, int NS>
 static void recurrence_launch_as(const RecParams& P, int num_seqs, cudaStream_t stream) {
   constexpr int CC = 128 / NS;
   const dim3 grid((P.vdim + CC - 1) / CC, P.H, num_seqs);
   const size_t smem = (size_t)(2 * kRecTok * NS * KPT + kRecTok * CC + 2 * kRecTok) * sizeof(float);
-  launch_pdl(linear_recurrence_kernel<T, KPT, NS>, grid, dim3(128), smem, stream, P);
+  launch_pdl(linear_recurrence_kernel<T, TV, KPT, NS>, grid, dim3(128), smem, stream, P);
 }
 
 // ------------------------------------------------------------------ the same recurrence, 16 tokens at a time
@@ -608,13 +615,13 @@ static int chunk_recurrence_launch(const RecParams& P, int num_seqs, cudaStream_
   return finish_launch();
 }
 
-template <typename T>
+template <typename T, typename TV = T>
 static int recurrence_launch(const RecParams& P, int num_seqs, cudaStream_t stream) {
-  if (P.kdim <= 16) recurrence_launch_as<T, 16, 1>(P, num_seqs, stream);
-  else if (P.kdim <= 32) recurrence_launch_as<T, 32, 1>(P, num_seqs, stream);
-  else if (P.kdim <= 64) recurrence_launch_as<T, 64, 1>(P, num_seqs, stream);
-  else if (P.kdim <= 128) recurrence_launch_as<T, 64, 2>(P, num_seqs, stream);
-  else recurrence_launch_as<T, 64, 4>(P, num_seqs, stream);
+  if (P.kdim <= 16) recurrence_launch_as<T, TV, 16, 1>(P, num_seqs, stream);
+  else if (P.kdim <= 32) recurrence_launch_as<T, TV, 32, 1>(P, num_seqs, stream);
+  else if (P.kdim <= 64) recurrence_launch_as<T, TV, 64, 1>(P, num_seqs, stream);
+  else if (P.kdim <= 128) recurrence_launch_as<T, TV, 64, 2>(P, num_seqs, stream);
+  else recurrence_launch_as<T, TV, 64, 4>(P, num_seqs, stream);
   return finish_launch();
 }
 
@@ -627,25 +634,26 @@ extern "C" int b200_attn_generic(void* out, const void* q, int64_t q_stride, con
                                  int32_t bt_stride, int32_t block_size, const int32_t* cu_q,
                                  const int32_t* cu_k, const int32_t* ctx_lens, int32_t num_seqs, int32_t max_q,
                                  int32_t num_heads, int32_t num_kv_heads, int32_t dim, int32_t vdim,
-                                 float scale, int32_t dtype, b200_stream_t stream) {
+                                 float scale, int32_t window, int32_t dtype, b200_stream_t stream) {
   B200_RETURN_IF(num_seqs < 0 || max_q < 0 || num_heads <= 0 || num_kv_heads <= 0 || dim <= 0 || vdim <= 0 ||
                      num_heads % num_kv_heads != 0, B200_ERR_BAD_SHAPE);
   B200_RETURN_IF(vdim > 32 * kAttnMaxVChunks, B200_ERR_UNSUPPORTED);
   if (num_seqs == 0 || max_q == 0) return B200_OK;
-  B200_RETURN_IF(!out || !q || !k || !v || (cu_q == nullptr) == (ctx_lens == nullptr) || (cu_q && !cu_k),
+  B200_RETURN_IF(!out || !q || !k || (cu_q == nullptr) == (ctx_lens == nullptr) || (cu_q && !cu_k),
                  B200_ERR_NULL_POINTER);
   B200_RETURN_IF(block_tables && block_size <= 0, B200_ERR_BAD_SHAPE);
+  B200_RETURN_IF(window < 0 || (!v && vdim > dim), B200_ERR_BAD_SHAPE);
   B200_RETURN_IF(!block_tables && !cu_q, B200_ERR_NULL_POINTER);       // decode rows read the paged cache
   const int rep = num_heads / num_kv_heads;
   const dim3 grid((max_q * rep + kAttnRows - 1) / kAttnRows, num_kv_heads, num_seqs);
-  const size_t smem = (size_t)(kAttnRows * dim + kAttnKeys * (dim + 1) + kAttnKeys * vdim) * sizeof(float);
+  const size_t smem = (size_t)(kAttnRows * dim + kAttnKeys * (dim + 1) + (v ? kAttnKeys * vdim : 0)) * sizeof(float);
   B200_RETURN_IF(smem > 200 * 1024, B200_ERR_UNSUPPORTED);
   B200_DISPATCH_3(dtype, T, {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(attn_generic_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_pdl(attn_generic_kernel<T>, grid, dim3(kAttnRows * 32), smem, (cudaStream_t)stream, (T*)out,
                (const T*)q, q_stride, (const T*)k, k_stride, (const T*)v, v_stride, block_tables, bt_stride,
-               block_size, cu_q, cu_k, ctx_lens, num_heads, num_kv_heads, dim, vdim, scale);
+               block_size, cu_q, cu_k, ctx_lens, num_heads, num_kv_heads, dim, vdim, scale, window);
   });
   return finish_launch();
 }
@@ -657,7 +665,7 @@ extern "C" int b200_linear_recurrence(float* out, const void* q, int64_t q_strid
                                       int32_t num_heads, int32_t groups, int32_t kdim, int32_t vdim, int32_t mode,
                                       int32_t act_silu, const float* decay, const void* dt, int64_t dt_stride,
                                       const float* dt_bias, const float* a_log, const float* d_skip,
-                                      int32_t dtype, b200_stream_t stream) {
+                                      int32_t qk_f32, int32_t dtype, b200_stream_t stream) {
   B200_RETURN_IF(num_seqs < 0 || num_heads <= 0 || groups <= 0 || num_heads % groups != 0 || kdim <= 0 ||
                      vdim <= 0 || (mode != 0 && mode != 1), B200_ERR_BAD_SHAPE);
   B200_RETURN_IF(kdim > 256, B200_ERR_UNSUPPORTED);
@@ -670,6 +678,12 @@ extern "C" int b200_linear_recurrence(float* out, const void* q, int64_t q_strid
   P.out = out, P.state = state, P.state_slots = state_slots, P.cu_q = cu_q, P.cu_k = cu_k, P.ctx_lens = ctx_lens;
   P.H = num_heads, P.groups = groups, P.kdim = kdim, P.vdim = vdim, P.mode = mode, P.act_silu = act_silu;
   P.decay = decay, P.dt = dt, P.dt_stride = dt_stride, P.dt_bias = dt_bias, P.a_log = a_log, P.d_skip = d_skip;
+  if (qk_f32 && dtype != B200_DTYPE_F32) {           // q, k already fp32 (rotated or normalised upstream), v as projected
+    B200_RETURN_IF(mode != 0, B200_ERR_UNSUPPORTED);
+    if (dtype == B200_DTYPE_BF16) return recurrence_launch<float, __nv_bfloat16>(P, num_seqs, (cudaStream_t)stream);
+    if (dtype == B200_DTYPE_F16) return recurrence_launch<float, __half>(P, num_seqs, (cudaStream_t)stream);
+    return B200_ERR_BAD_DTYPE;
+  }
   if (chunk_recurrence_ok(P, dtype, max_q)) return chunk_recurrence_launch(P, num_seqs, (cudaStream_t)stream);
   B200_DISPATCH_3(dtype, T, return recurrence_launch<T>(P, num_seqs, (cudaStream_t)stream));
   return B200_OK;

@@ -1,0 +1,386 @@
+// stream_ops.cu -- row-wise kernels of decoders that keep SEVERAL residual streams (hyper-connections), rotate
+// parts of their heads, or feed a recurrence with fp32 unit vectors and per-channel decays:
+//
+//   stream_mix_norm     x_t <- sum_s mix[s][t] x_s + out[t] y for all streams at once, then u = sum_t in[t] x_t and
+//                       h = norm(u): the "residual add + next pre-norm" of a multi-stream residual in ONE launch.
+//                       norm is a layer norm with weight and bias, or an RMS norm with a (offset + w) weight.
+//   rotary_heads        rotary positions on the first `dims` columns of every head (pairs (2i, 2i+1) or
+//                       (i, i + dims/2)), a scale per head range, output in fp32 or the element type, with free
+//                       input/output head strides (so that a rotated part can be written into a wider head).
+//   delta_prep          what a gated delta rule reads besides v: q and k as fp32 unit vectors (q scaled), the
+//                       per-channel decay exp(-exp(A) softplus(a + bias)) and beta = sigmoid(b), all fp32.
+//   latent_kv_prep      RMS norm of the query latent; RMS norm of the key/value latent and rotation of the shared
+//                       rotated key, written as one cache row [latent | rotated key] (packed and/or paged).
+//   glu_clamped         min(g, L) sigmoid(alpha min(g, L)) (clamp(u, -L, L) + 1) for a gated feed-forward.
+//
+// All arithmetic is fp32 (angles in fp64: a position times a frequency loses digits in fp32 at long range).
+#include "seq_common.cuh"
+
+namespace b200 {
+
+constexpr int kMaxStreams = 8;
+
+struct StreamMixParams {
+  float* x;               // [rows, S, hidden] fp32 streams, updated in place
+  const void* y;          // [rows, hidden] sublayer output (element type) or nullptr: no update
+  const float* mix;       // [S, S] (from, to) or nullptr with y == nullptr
+  const float* out_w;     // [S]
+  const float* in_w;      // [S] read weights of the NEXT sublayer (nullptr: all ones, the sum of the streams)
+  const float* w;         // [hidden] norm weight (nullptr: no h is produced)
+  const float* b;         // [hidden] norm bias (layer norm) or nullptr
+  void* h;                // [rows, hidden] element type
+  float* sum_out;         // optional [rows, hidden] fp32: u itself (before the norm)
+  float eps, offset;
+  int S, hidden, kind;    // kind 0: layer norm (w, b); 1: RMS norm, weight offset + w
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+stream_mix_norm_kernel(const StreamMixParams P) {
+  extern __shared__ float su[];                       // [hidden]
+  __shared__ float red[32];
+  __shared__ float smix[kMaxStreams * kMaxStreams], sout[kMaxStreams], sin_[kMaxStreams];
+  pdl_wait();
+  const int S = P.S, hidden = P.hidden;
+  if (threadIdx.x < S * S) smix[threadIdx.x] = P.mix != nullptr ? P.mix[threadIdx.x] : 0.f;
+  if (threadIdx.x < S) {
+    sout[threadIdx.x] = P.out_w != nullptr ? P.out_w[threadIdx.x] : 0.f;
+    sin_[threadIdx.x] = P.in_w != nullptr ? P.in_w[threadIdx.x] : 1.f;
+  }
+  __syncthreads();
+  float* xr = P.x + (int64_t)blockIdx.x * S * hidden;
+  const T* yr = P.y != nullptr ? (const T*)P.y + (int64_t)blockIdx.x * hidden : nullptr;
+  float part = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float xs[kMaxStreams];
+#pragma unroll
+    for (int s = 0; s < kMaxStreams; ++s) xs[s] = s < S ? xr[(int64_t)s * hidden + i] : 0.f;
+    float u = 0.f;
+    if (yr != nullptr) {
+      const float y = to_f32<T>(yr[i]);
+#pragma unroll
+      for (int t = 0; t < kMaxStreams; ++t) {
+        if (t < S) {
+          float acc = 0.f;
+#pragma unroll
+          for (int s = 0; s < kMaxStreams; ++s)
+            if (s < S) acc += smix[s * S + t] * xs[s];
+          acc += sout[t] * y;
+          xr[(int64_t)t * hidden + i] = acc;
+          u += sin_[t] * acc;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int t = 0; t < kMaxStreams; ++t)
+        if (t < S) u += sin_[t] * xs[t];
+    }
+    su[i] = u;
+    part += P.kind == 0 ? u : u * u;
+  }
+  if (P.sum_out != nullptr)
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) P.sum_out[(int64_t)blockIdx.x * hidden + i] = su[i];
+  if (P.w == nullptr) return;
+  T* h = (T*)P.h + (int64_t)blockIdx.x * hidden;
+  if (P.kind == 0) {
+    const float mean = cta_sum(part, red) / (float)hidden;
+    float sq = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      const float d = su[i] - mean;
+      sq += d * d;
+    }
+    const float rstd = 1.0f / sqrtf(cta_sum(sq, red) / (float)hidden + P.eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+      h[i] = from_f32<T>((su[i] - mean) * rstd * P.w[i] + (P.b != nullptr ? P.b[i] : 0.f));
+  } else {
+    const float rstd = 1.0f / sqrtf(cta_sum(part, red) / (float)hidden + P.eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) h[i] = from_f32<T>(su[i] * rstd * (P.offset + P.w[i]));
+  }
+}
+
+// ------------------------------------------------------------------ rotary positions
+struct RotaryParams {
+  const void* in;          // element type; head hd of token t starts at in + t * in_stride + hd * in_head
+  void* out;               // fp32 or element type; head hd of token t at out + t * out_stride + hd * out_head
+  int64_t in_stride, out_stride;
+  int in_head, out_head;
+  const int64_t* positions;
+  int tokens, heads, width, dims, interleaved, split, out_f32;
+  float scale_lo, scale_hi;   // heads < split are multiplied by scale_lo, the others by scale_hi
+  double log2_base;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+rotary_heads_kernel(const RotaryParams P) {
+  pdl_wait();
+  const int half = P.dims / 2;
+  const int per_tok = half + (P.width - P.dims);      // work items per token: pairs, then pass-through columns
+  const int64_t total = (int64_t)P.tokens * per_tok;
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    const int t = (int)(e / per_tok), w = (int)(e % per_tok);
+    const T* src = (const T*)P.in + (int64_t)t * P.in_stride;
+    float* of = (float*)P.out + (int64_t)t * P.out_stride;
+    T* ot = (T*)P.out + (int64_t)t * P.out_stride;
+    if (w < half) {
+      const double f = exp2(-(2.0 * (double)w / (double)P.dims) * P.log2_base);
+      double sn, cs;
+      sincos((double)P.positions[t] * f, &sn, &cs);
+      const float c = (float)cs, s = (float)sn;
+      const int a = P.interleaved ? 2 * w : w, b = P.interleaved ? 2 * w + 1 : w + half;
+      for (int hd = 0; hd < P.heads; ++hd) {
+        const float sc = hd < P.split ? P.scale_lo : P.scale_hi;
+        const float u = to_f32<T>(src[(int64_t)hd * P.in_head + a]), v = to_f32<T>(src[(int64_t)hd * P.in_head + b]);
+        const float ra = (u * c - v * s) * sc, rb = (v * c + u * s) * sc;
+        if (P.out_f32) {
+          of[(int64_t)hd * P.out_head + a] = ra;
+          of[(int64_t)hd * P.out_head + b] = rb;
+        } else {
+          ot[(int64_t)hd * P.out_head + a] = from_f32<T>(ra);
+          ot[(int64_t)hd * P.out_head + b] = from_f32<T>(rb);
+        }
+      }
+    } else {
+      const int col = P.dims + (w - half);
+      for (int hd = 0; hd < P.heads; ++hd) {
+        const float sc = hd < P.split ? P.scale_lo : P.scale_hi;
+        const float u = to_f32<T>(src[(int64_t)hd * P.in_head + col]) * sc;
+        if (P.out_f32) of[(int64_t)hd * P.out_head + col] = u;
+        else ot[(int64_t)hd * P.out_head + col] = from_f32<T>(u);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ inputs of a gated delta rule
+// One warp per (token, unit): units 0 .. 2G-1 are the q and k heads (unit vectors), units 2G .. 2G+H-1 the decay
+// rows of the heads (and beta).
+template <typename T>
+__global__ void __launch_bounds__(256)
+delta_prep_kernel(float* __restrict__ qk, float* __restrict__ decay, float* __restrict__ beta,
+                  const T* __restrict__ qk_in, int64_t qk_stride, const T* __restrict__ a, int64_t a_stride,
+                  const T* __restrict__ b, int64_t b_stride, const float* __restrict__ dt_bias,
+                  const float* __restrict__ a_log, int tokens, int H, int G, int dim, float unit_eps, float q_scale) {
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int per_tok = 2 * G + H;
+  if (unit >= (int64_t)tokens * per_tok) return;
+  const int t = (int)(unit / per_tok), u = (int)(unit % per_tok);
+  if (u < 2 * G) {
+    const T* x = qk_in + (int64_t)t * qk_stride + (int64_t)u * dim;
+    float ss = 0.f;
+    for (int i = lane; i < dim; i += 32) {
+      const float v = to_f32<T>(x[i]);
+      ss += v * v;
+    }
+    const float mul = (u < G ? q_scale : 1.0f) / sqrtf(warp_sum(ss) + unit_eps);
+    float* o = qk + (int64_t)t * (2 * G * dim) + (int64_t)u * dim;
+    for (int i = lane; i < dim; i += 32) o[i] = to_f32<T>(x[i]) * mul;
+    return;
+  }
+  const int h = u - 2 * G;
+  const float rate = expf(a_log[h]);
+  const T* ar = a + (int64_t)t * a_stride + (int64_t)h * dim;
+  float* o = decay + (int64_t)t * ((int64_t)H * dim) + (int64_t)h * dim;
+  for (int i = lane; i < dim; i += 32)
+    o[i] = expf(-rate * softplus_f(to_f32<T>(ar[i]) + dt_bias[(int64_t)h * dim + i]));
+  if (lane == 0) beta[(int64_t)t * H + h] = sigmoid_f(to_f32<T>(b[(int64_t)t * b_stride + h]));
+}
+
+// ------------------------------------------------------------------ latents of a latent attention
+// One CTA per token. cq = rms(dq) * wq (element type); row = [rms(c) * wc | rotate(kr)] (element type) into `kc`
+// (packed, [tokens, rank + rot]) and, when slots are given, into the paged cache row of the token.
+template <typename T>
+__global__ void __launch_bounds__(128)
+latent_kv_prep_kernel(T* __restrict__ cq, T* __restrict__ kc, T* __restrict__ cache, const int* __restrict__ slots,
+                      int slot_pairs, int block_size, const T* __restrict__ dq, int64_t dq_stride,
+                      const T* __restrict__ dkv, int64_t dkv_stride, const float* __restrict__ wq,
+                      const float* __restrict__ wc, const int64_t* __restrict__ positions, int q_rank, int rank,
+                      int rot, int dims, int interleaved, double log2_base, float eps) {
+  __shared__ float red[32];
+  pdl_wait();
+  const int64_t t = blockIdx.x;
+  const T* q = dq + t * dq_stride;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < q_rank; i += blockDim.x) {
+    const float v = to_f32<T>(q[i]);
+    ss += v * v;
+  }
+  float rstd = 1.0f / sqrtf(cta_sum(ss, red) / (float)q_rank + eps);
+  for (int i = threadIdx.x; i < q_rank; i += blockDim.x)
+    cq[t * q_rank + i] = from_f32<T>(to_f32<T>(q[i]) * rstd * wq[i]);
+
+  const T* c = dkv + t * dkv_stride;
+  ss = 0.f;
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) {
+    const float v = to_f32<T>(c[i]);
+    ss += v * v;
+  }
+  rstd = 1.0f / sqrtf(cta_sum(ss, red) / (float)rank + eps);
+  const int row = rank + rot;
+  T* dst = nullptr;
+  if (cache != nullptr) {
+    const int64_t slot = slot_pairs ? (int64_t)slots[2 * t] * block_size + slots[2 * t + 1] : (int64_t)slots[t];
+    if (slot >= 0) dst = cache + slot * row;
+  }
+  T* pk = kc != nullptr ? kc + t * row : nullptr;
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) {
+    const T v = from_f32<T>(to_f32<T>(c[i]) * rstd * wc[i]);
+    if (pk != nullptr) pk[i] = v;
+    if (dst != nullptr) dst[i] = v;
+  }
+  const int half = dims / 2;
+  for (int w = threadIdx.x; w < half + (rot - dims); w += blockDim.x) {
+    if (w < half) {
+      const double f = exp2(-(2.0 * (double)w / (double)dims) * log2_base);
+      double sn, cs;
+      sincos((double)positions[t] * f, &sn, &cs);
+      const float cc = (float)cs, s = (float)sn;
+      const int a = interleaved ? 2 * w : w, b = interleaved ? 2 * w + 1 : w + half;
+      const float u = to_f32<T>(c[rank + a]), v = to_f32<T>(c[rank + b]);
+      const T ra = from_f32<T>(u * cc - v * s), rb = from_f32<T>(v * cc + u * s);
+      if (pk != nullptr) pk[rank + a] = ra, pk[rank + b] = rb;
+      if (dst != nullptr) dst[rank + a] = ra, dst[rank + b] = rb;
+    } else {
+      const int col = dims + (w - half);
+      if (pk != nullptr) pk[rank + col] = c[rank + col];
+      if (dst != nullptr) dst[rank + col] = c[rank + col];
+    }
+  }
+}
+
+// ------------------------------------------------------------------ clamped gated unit
+template <typename T>
+__global__ void __launch_bounds__(256)
+glu_clamped_kernel(T* __restrict__ out, const T* __restrict__ x, int64_t rows, int inter, float alpha, float limit) {
+  pdl_wait();
+  const int64_t total = rows * inter;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / inter;
+    const int c = (int)(i - r * inter);
+    const float g = fminf(to_f32<T>(x[r * 2 * inter + c]), limit);
+    const float u = fminf(fmaxf(to_f32<T>(x[r * 2 * inter + inter + c]), -limit), limit);
+    out[i] = from_f32<T>(g * sigmoid_f(alpha * g) * (u + 1.0f));
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+glu_clamped_vec_kernel(T* __restrict__ out, const T* __restrict__ x, int64_t rows, int inter8, float alpha,
+                       float limit) {
+  pdl_wait();
+  const int64_t total = rows * inter8;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / inter8;
+    const int c = (int)(i - r * inter8);
+    float g[8], u[8], o[8];
+    load8<T>(x + (r * 2 * inter8 + c) * 8, g);
+    load8<T>(x + (r * 2 * inter8 + inter8 + c) * 8, u);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float gg = fminf(g[e], limit), uu = fminf(fmaxf(u[e], -limit), limit);
+      o[e] = gg * sigmoid_f(alpha * gg) * (uu + 1.0f);
+    }
+    store8<T>(out + i * 8, o);
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_stream_mix_norm(void* h, float* x, const void* y, const float* mix, const float* out_w,
+                                    const float* in_w, const float* w, const float* b, float* sum_out,
+                                    float eps, float offset, int32_t kind, int32_t rows, int32_t streams,
+                                    int32_t hidden, int32_t dtype, b200_stream_t stream) {
+  B200_RETURN_IF(rows < 0 || streams <= 0 || hidden <= 0 || (kind != 0 && kind != 1), B200_ERR_BAD_SHAPE);
+  B200_RETURN_IF(streams > kMaxStreams || hidden > 48 * 1024, B200_ERR_UNSUPPORTED);
+  if (rows == 0) return B200_OK;
+  B200_RETURN_IF(!x || (y && (!mix || !out_w)) || (w && !h), B200_ERR_NULL_POINTER);
+  StreamMixParams P;
+  P.x = x, P.y = y, P.mix = mix, P.out_w = out_w, P.in_w = in_w, P.w = w, P.b = b, P.h = h, P.sum_out = sum_out;
+  P.eps = eps, P.offset = offset, P.S = streams, P.hidden = hidden, P.kind = kind;
+  const size_t smem = (size_t)hidden * sizeof(float);
+  B200_DISPATCH_3(dtype, T, {
+    if (smem > 40 * 1024)
+      cudaFuncSetAttribute(stream_mix_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_pdl(stream_mix_norm_kernel<T>, dim3(rows), dim3(256), smem, (cudaStream_t)stream, P);
+  });
+  return finish_launch();
+}
+
+extern "C" int b200_rotary_heads(void* out, int64_t out_stride, int32_t out_head, int32_t out_f32, const void* in,
+                                 int64_t in_stride, int32_t in_head, const int64_t* positions, int32_t tokens,
+                                 int32_t heads, int32_t width, int32_t dims, double base, int32_t interleaved,
+                                 int32_t split, float scale_lo, float scale_hi, int32_t dtype,
+                                 b200_stream_t stream) {
+  B200_RETURN_IF(tokens < 0 || heads <= 0 || width <= 0 || dims < 0 || dims > width || dims % 2 != 0 || base <= 0.0,
+                 B200_ERR_BAD_SHAPE);
+  if (tokens == 0) return B200_OK;
+  B200_RETURN_IF(!out || !in || !positions, B200_ERR_NULL_POINTER);
+  RotaryParams P;
+  P.in = in, P.out = out, P.in_stride = in_stride, P.out_stride = out_stride, P.in_head = in_head;
+  P.out_head = out_head, P.positions = positions, P.tokens = tokens, P.heads = heads, P.width = width;
+  P.dims = dims, P.interleaved = interleaved, P.split = split, P.out_f32 = out_f32, P.scale_lo = scale_lo;
+  P.scale_hi = scale_hi, P.log2_base = log2(base);
+  const int64_t total = (int64_t)tokens * (dims / 2 + (width - dims));
+  int grid = (int)((total + 255) / 256);
+  if (grid > 148 * 16) grid = 148 * 16;
+  B200_DISPATCH_3(dtype, T, launch_pdl(rotary_heads_kernel<T>, dim3(grid), dim3(256), 0, (cudaStream_t)stream, P));
+  return finish_launch();
+}
+
+extern "C" int b200_delta_prep(float* qk, float* decay, float* beta, const void* qk_in, int64_t qk_stride,
+                               const void* a, int64_t a_stride, const void* b, int64_t b_stride,
+                               const float* dt_bias, const float* a_log, int32_t tokens, int32_t num_heads,
+                               int32_t groups, int32_t dim, float unit_eps, float q_scale, int32_t dtype,
+                               b200_stream_t stream) {
+  B200_RETURN_IF(tokens < 0 || num_heads <= 0 || groups <= 0 || dim <= 0, B200_ERR_BAD_SHAPE);
+  if (tokens == 0) return B200_OK;
+  B200_RETURN_IF(!qk || !decay || !beta || !qk_in || !a || !b || !dt_bias || !a_log, B200_ERR_NULL_POINTER);
+  const int64_t units = (int64_t)tokens * (2 * groups + num_heads);
+  const dim3 grid((unsigned)((units + 7) / 8));
+  B200_DISPATCH_3(dtype, T, launch_pdl(delta_prep_kernel<T>, grid, dim3(256), 0, (cudaStream_t)stream, qk, decay, beta,
+                                       (const T*)qk_in, qk_stride, (const T*)a, a_stride, (const T*)b, b_stride,
+                                       dt_bias, a_log, tokens, num_heads, groups, dim, unit_eps, q_scale));
+  return finish_launch();
+}
+
+extern "C" int b200_latent_kv_prep(void* cq, void* kc, void* cache, const int32_t* slots, int32_t slot_pairs,
+                                   int32_t block_size, const void* dq, int64_t dq_stride, const void* dkv,
+                                   int64_t dkv_stride, const float* wq, const float* wc, const int64_t* positions,
+                                   int32_t tokens, int32_t q_rank, int32_t rank, int32_t rot, int32_t dims,
+                                   double base, int32_t interleaved, float eps, int32_t dtype,
+                                   b200_stream_t stream) {
+  B200_RETURN_IF(tokens < 0 || q_rank <= 0 || rank <= 0 || rot < 0 || dims < 0 || dims > rot || dims % 2 != 0 ||
+                     base <= 0.0, B200_ERR_BAD_SHAPE);
+  if (tokens == 0) return B200_OK;
+  B200_RETURN_IF(!cq || !dq || !dkv || !wq || !wc || !positions || (cache && !slots), B200_ERR_NULL_POINTER);
+  B200_DISPATCH_3(dtype, T, launch_pdl(latent_kv_prep_kernel<T>, dim3(tokens), dim3(128), 0, (cudaStream_t)stream,
+                                       (T*)cq, (T*)kc, (T*)cache, slots, slot_pairs, block_size, (const T*)dq,
+                                       dq_stride, (const T*)dkv, dkv_stride, wq, wc, positions, q_rank, rank, rot,
+                                       dims, interleaved, log2(base), eps));
+  return finish_launch();
+}
+
+extern "C" int b200_glu_clamped(void* out, const void* x, int32_t rows, int32_t inter, float alpha, float limit,
+                                int32_t dtype, b200_stream_t stream) {
+  B200_RETURN_IF(rows < 0 || inter <= 0, B200_ERR_BAD_SHAPE);
+  if (rows == 0) return B200_OK;
+  B200_RETURN_IF(!out || !x, B200_ERR_NULL_POINTER);
+  if (inter % 8 == 0 && aligned16(out) && aligned16(x)) {
+    const int64_t vecs = (int64_t)rows * (inter / 8);
+    int vgrid = (int)((vecs + 255) / 256);
+    if (vgrid > 148 * 16) vgrid = 148 * 16;
+    B200_DISPATCH_3(dtype, T, launch_pdl(glu_clamped_vec_kernel<T>, dim3(vgrid), dim3(256), 0, (cudaStream_t)stream,
+                                         (T*)out, (const T*)x, (int64_t)rows, inter / 8, alpha, limit));
+    return finish_launch();
+  }
+  const int64_t total = (int64_t)rows * inter;
+  int grid = (int)((total + 255) / 256);
+  if (grid > 148 * 16) grid = 148 * 16;
+  B200_DISPATCH_3(dtype, T, launch_pdl(glu_clamped_kernel<T>, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (T*)out,
+                                       (const T*)x, (int64_t)rows, inter, alpha, limit));
+  return finish_launch();
+}

@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_char_p, c_float, c_int32, c_int64, c_size_t, c_uint64, c_void_p
+from ctypes import c_char_p, c_double, c_float, c_int32, c_int64, c_size_t, c_uint64, c_void_p
 
 _LIB_ENV = "B200ATTN_LIB"
 _HERE = os.path.dirname(os.path.abspath(__file__))
@@ -114,11 +114,34 @@ PROTOTYPES = {
     "b200_act_and_mul": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_void_p]),
     "b200_attn_generic": (c_int32, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p,
                                     c_int32, c_int32, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,
-                                    c_int32, c_int32, c_int32, c_float, c_int32, c_void_p]),
+                                    c_int32, c_int32, c_int32, c_float, c_int32, c_int32, c_void_p]),
     "b200_linear_recurrence": (c_int32, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64,
                                          c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,
                                          c_int32, c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p,
-                                         c_int64, c_void_p, c_void_p, c_void_p, c_int32, c_void_p]),
+                                         c_int64, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_void_p]),
+    # multi-stream residual, rotary, delta rule, latent attention, clamped unit, generic MoE
+    "b200_stream_mix_norm": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                       c_void_p, c_void_p, c_float, c_float, c_int32, c_int32, c_int32, c_int32,
+                                       c_int32, c_void_p]),
+    "b200_rotary_heads": (c_int32, [c_void_p, c_int64, c_int32, c_int32, c_void_p, c_int64, c_int32, c_void_p,
+                                    c_int32, c_int32, c_int32, c_int32, c_double, c_int32, c_int32, c_float,
+                                    c_float, c_int32, c_void_p]),
+    "b200_delta_prep": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p,
+                                  c_int64, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32, c_float,
+                                  c_float, c_int32, c_void_p]),
+    "b200_delta_rule": (c_int32, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p,
+                                  c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32,
+                                  c_int32, c_int32, c_int32, c_int32, c_void_p]),
+    "b200_latent_kv_prep": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_void_p, c_int64,
+                                      c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,
+                                      c_int32, c_int32, c_double, c_int32, c_float, c_int32, c_void_p]),
+    "b200_glu_clamped": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_float, c_float, c_int32, c_void_p]),
+    "b200_moe_route_grouped": (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int32, c_int32,
+                                         c_int32, c_int32, c_int32, c_float, c_void_p]),
+    "b200_moe_gemm_generic": (c_int32, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int32,
+                                        c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_void_p]),
+    "b200_moe_combine_weighted": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,
+                                            c_int32, c_void_p]),
     "b200_sample": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int64, c_uint64,
                               c_uint64, c_void_p, c_int32, c_void_p]),
 }

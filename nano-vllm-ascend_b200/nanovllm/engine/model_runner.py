@@ -28,7 +28,7 @@ from ..config import Config, GraphMode
 from ..layers.sampler import Sampler
 from ..models.models_map import model_dict
 from ..utils.context import get_context, reset_context, set_context
-from ..utils.loader import device_init, load_model, seeded_init
+from ..utils.loader import checkpoint_shapes, device_init, load_model, seeded_init
 from .sequence import Sequence
 
 _SHM_PREFIX = "nano_vllm_b200"
@@ -91,6 +91,11 @@ class ModelRunner:
             torch.backends.cuda.matmul.allow_tf32 = False
             torch.backends.cudnn.allow_tf32 = False
             torch.set_float32_matmul_precision("highest")
+        has_ckpt = os.path.isdir(config.model) and any(
+            f.endswith(".safetensors") for f in os.listdir(config.model))
+        if has_ckpt and getattr(model_dict[arch], "reads_checkpoint_shapes", False):
+            # sizes that the configuration leaves to the tensors (inner sizes of low-rank projections)
+            self.hf_config.checkpoint_shapes = checkpoint_shapes(config.model)
         prev = torch.get_default_dtype()
         torch.set_default_dtype(self.dtype)
         try:
@@ -98,8 +103,6 @@ class ModelRunner:
                 self.model = model_dict[arch](self.hf_config)
         finally:
             torch.set_default_dtype(prev)
-        has_ckpt = os.path.isdir(config.model) and any(
-            f.endswith(".safetensors") for f in os.listdir(config.model))
         if config.load_weights if config.load_weights is not None else has_ckpt:
             load_model(self.model, config.model)
         else:

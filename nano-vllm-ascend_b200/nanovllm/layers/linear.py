@@ -116,6 +116,39 @@ class MergedColumnParallelLinear(ColumnParallelLinear):
         param.data.narrow(self.tp_dim, start, size).copy_(piece)
 
 
+class PaddedMergedLinear(ReplicatedLinear):
+    """Several small matrices that read the same input, stacked with each part padded to a multiple of 8 rows (so
+    that every part of the output starts on a 16-byte boundary) and, for ``pad_input``, the input columns padded
+    to a multiple of 8 as well (the consumer of a padded part). Padding stays zero. Not sharded."""
+
+    def __init__(self, input_size, output_sizes, pad_input=False):
+        self.output_sizes = list(output_sizes)
+        self.padded_sizes = [-(-n // 8) * 8 for n in self.output_sizes]
+        self.true_input = input_size
+        super().__init__(-(-input_size // 8) * 8 if pad_input else input_size, sum(self.padded_sizes))
+        self.weight.data.zero_()
+
+    def part(self, y, i):
+        """Columns of output y that belong to part i (without its padding)."""
+        start = sum(self.padded_sizes[:i])
+        return y[:, start:start + self.output_sizes[i]]
+
+    def padded_part(self, y, i):
+        start = sum(self.padded_sizes[:i])
+        return y[:, start:start + self.padded_sizes[i]]
+
+    def zero_padding(self):
+        off = 0
+        for n, pad in zip(self.output_sizes, self.padded_sizes):
+            self.weight.data[off + n:off + pad].zero_()
+            off += pad
+        self.weight.data[:, self.true_input:].zero_()
+
+    def weight_loader(self, param, loaded_weight, loaded_shard_id: int = 0):
+        start = sum(self.padded_sizes[:loaded_shard_id])
+        param.data[start:start + loaded_weight.shape[0], :loaded_weight.shape[1]].copy_(loaded_weight)
+
+
 class QKVParallelLinear(ColumnParallelLinear):
     """Fused q|k|v projection; each rank holds H/tp query heads and Hkv/tp kv heads."""
 

@@ -101,3 +101,40 @@ class SparseMoeBlock(nn.Module):
         if self.ep_size > 1 and tp_collectives():
             dist.all_reduce(y)
         return y
+
+
+class GroupedSigmoidMoe(nn.Module):
+    """Mixture of experts with a sigmoid router: choice scores are sigmoid(z) plus a stored correction, experts form
+    ``groups`` equal groups of neighbours of which only the ``keep`` best (by the sum of their two largest choice
+    scores) stay in play, ``top_k`` experts are chosen and weighted by their sigmoid scores, normalised and scaled.
+    The router runs in fp32 (ops.moe_route_grouped); experts are gate/up/down MLPs with silu, stacked in two tensors.
+    16-bit models whose sizes fit the tensor-core kernels of csrc/moe.cu run the expert GEMMs there, everything else
+    (fp32, other sizes) on the generic kernels of csrc/moe_generic.cu with fp32 routing weights."""
+
+    def __init__(self, hidden_size: int, inter: int, num_experts: int, top_k: int, groups: int = 1, keep: int = 1,
+                 scale: float = 1.0):
+        super().__init__()
+        if tp_rank_size()[1] != 1:
+            raise ValueError("GroupedSigmoidMoe holds every expert on one GPU")
+        self.hidden_size, self.inter, self.num_experts, self.top_k = hidden_size, inter, num_experts, top_k
+        self.groups, self.keep, self.scale = groups, keep, scale
+        self.router = nn.Parameter(torch.empty(num_experts, hidden_size, dtype=torch.float32))
+        self.correction = nn.Parameter(torch.zeros(num_experts, dtype=torch.float32))
+        self.w13 = nn.Parameter(torch.empty(num_experts, 2 * inter, hidden_size))
+        self.w2 = nn.Parameter(torch.empty(num_experts, hidden_size, inter))
+        self.w13.weight_loader = self._load_w13
+        self.w2.weight_loader = lambda p, w, e: p.data[e].copy_(w)
+        self.fast = True           # False: always the generic kernels
+
+    def _load_w13(self, param, loaded, shard):
+        e, part = shard                                                  # part 0: gate rows, 1: up rows
+        param.data[e, part * self.inter:(part + 1) * self.inter].copy_(loaded)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        logits = F.linear(x.float(), self.router)
+        ids, w = ops.moe_route_grouped(logits, self.correction, self.top_k, self.groups, self.keep, self.scale)
+        plan = ops.moe_align(ids, 0, self.num_experts)
+        if (self.fast and x.dtype != torch.float32 and self.hidden_size % 128 == 0 and self.inter % 64 == 0
+                and self.top_k <= 8 and self.num_experts <= 256):
+            return ops.moe_experts(x, self.w13, self.w2, ids, w.to(x.dtype), plan)
+        return ops.moe_experts_generic(x, self.w13, self.w2, w, plan)

@@ -1,6 +1,8 @@
 """Building blocks of hybrid decoders: a short causal convolution with a carried tail, linear recurrences
-with an fp32 state (constant decay per head, or the selective state-space form), the gated norms that follow
-them, and causal softmax attention whose key and value sizes may differ.
+with an fp32 state (constant decay per head, the selective state-space form, or the gated delta rule with a decay
+per key channel), the gated norms that follow them, rotary positions on part of a head, causal softmax attention
+whose key and value sizes may differ (optionally inside a sliding window), attention over a cached latent, and the
+mixing weights of a residual that is kept in several streams.
 
 Every block reads the step's ``Context`` (which tokens belong to which sequence, their cache slots and
 state slots) and runs on the kernels of ``csrc/seq_ops.cu`` / ``csrc/seq_mixers.cu``. Per-sequence state is
@@ -83,6 +85,7 @@ class LinearRecurrence(nn.Module):
         return {"state": ((self.num_heads, self.kdim, self.vdim), F32)}
 
     def forward(self, q, k, v, dt=None) -> torch.Tensor:
+        """q and k may be fp32 beside 16-bit v (constant-decay form): rotated or normalised in 32-bit upstream."""
         ctx, spans, bound = _spans_and_slots(self.state)
         kw = dict(decay=self.decay, act_silu=self.act_silu) if self.decay is not None else dict(
             dt=dt, dt_bias=self.dt_bias, a_log=self.A_log, d_skip=self.D)
@@ -113,9 +116,10 @@ class VarSizeAttention(nn.Module):
     caller's fused epilogue). 16-bit models with dim == vdim in {64, 128} run on the tcgen05 prefill kernel and
     the paged decode kernel of the dense decoders; everything else (other sizes, fp32) on the generic kernel."""
 
-    def __init__(self, num_heads: int, num_kv_heads: int, dim: int, vdim: int, scale: float):
+    def __init__(self, num_heads: int, num_kv_heads: int, dim: int, vdim: int, scale: float, window: int = 0):
         super().__init__()
         self.num_heads, self.num_kv_heads, self.dim, self.vdim, self.scale = num_heads, num_kv_heads, dim, vdim, scale
+        self.window = int(window)                       # > 0: position i sees keys j with 0 <= i - j < window
         self.k_cache = torch.tensor([])
         self.v_cache = torch.tensor([])
         self.layer_id = -1
@@ -126,7 +130,7 @@ class VarSizeAttention(nn.Module):
 
     def _fast(self, q) -> bool:
         rep, G = self.num_heads // self.num_kv_heads, self.num_kv_heads
-        return (not self.force_generic and q.dtype in (torch.bfloat16, torch.float16) and self.dim == self.vdim
+        return (not self.force_generic and not self.window and q.dtype in (torch.bfloat16, torch.float16) and self.dim == self.vdim
                 and self.dim in (64, 128) and rep <= 8 and (G in (1, 2, 4) or G % 8 == 0))
 
     def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
@@ -147,5 +151,103 @@ class VarSizeAttention(nn.Module):
         spans = ops.StepSpans.of(ctx)
         if paged:
             return ops.attn_generic(q, self.k_cache, self.v_cache, spans, self.scale, self.num_kv_heads, self.vdim,
-                                    block_tables=ctx.block_tables)
-        return ops.attn_generic(q, k, v, spans, self.scale, self.num_kv_heads, self.vdim)
+                                    block_tables=ctx.block_tables, window=self.window)
+        return ops.attn_generic(q, k, v, spans, self.scale, self.num_kv_heads, self.vdim, window=self.window)
+
+
+class DeltaRule(nn.Module):
+    """Gated delta rule with one decay per head and key channel, state S fp32 [kdim, vdim] per head in ``state``:
+    S <- diag(g) S; w = beta (v - S^T k); S <- S + k w^T; o = S^T q, with g = exp(-exp(A_log_h) softplus(a + dt_bias)),
+    beta = sigmoid(b), q and k divided by sqrt(sum x^2 + unit_eps) per head and q times ``q_scale``. Everything but the
+    projected activations is fp32."""
+
+    def __init__(self, num_heads: int, groups: int, kdim: int, vdim: int, unit_eps: float = 1e-6,
+                 q_scale: float | None = None):
+        super().__init__()
+        self.num_heads, self.groups, self.kdim, self.vdim = num_heads, groups, kdim, vdim
+        self.unit_eps = unit_eps
+        self.q_scale = kdim ** -0.5 if q_scale is None else q_scale
+        self.A_log, self.dt_bias = small_param(num_heads), small_param(num_heads * kdim)
+        self.state = None
+
+    def state_shapes(self):
+        return {"state": ((self.num_heads, self.kdim, self.vdim), F32)}
+
+    def forward(self, qk, v, a, b) -> torch.Tensor:
+        """qk [T, 2*groups*kdim] (q heads, then k heads), v [T, H*vdim], a [T, H*kdim], b [T, H] -> fp32 [T, H*vdim]."""
+        ctx, spans, bound = _spans_and_slots(self.state)
+        qk32, g, beta = ops.delta_prep(qk, a, b, self.dt_bias, self.A_log, self.num_heads, self.groups, self.kdim,
+                                       self.unit_eps, self.q_scale)
+        n = self.groups * self.kdim
+        return ops.delta_rule(qk32[:, :n], qk32[:, n:], v, g, beta, spans, self.num_heads, self.groups, self.kdim,
+                              self.vdim, self.state if bound else None, ctx.state_slots if bound else None)
+
+
+class Rotary:
+    """Rotary positions on the first ``dims`` columns of a head: angle pos * base^(-2i/dims), pairs (2i, 2i+1)
+    (``interleaved``) or (i, i + dims/2). Constants only; the kernel computes the angles in fp64."""
+
+    def __init__(self, dims: int, base: float, interleaved: bool):
+        self.dims, self.base, self.interleaved = int(dims), float(base), bool(interleaved)
+
+    def __call__(self, x, positions, out=None, out_f32=False, split=0, scale_lo=1.0, scale_hi=1.0):
+        """x [T, heads, width] view -> rotated (and scaled) copy, see ops.rotary_heads."""
+        return ops.rotary_heads(x, positions, x.shape[1], x.shape[2], self.dims, self.base, self.interleaved, out=out,
+                                out_f32=out_f32, split=split, scale_lo=scale_lo, scale_hi=scale_hi)
+
+
+class LatentAttention(nn.Module):
+    """Softmax attention whose keys and values are up-projections of ONE cached latent row per token:
+    score_h(i, j) = scale (q_h^plain . W_uk,h c_j + q_h^rot . r_j), value_h(j) = W_uv,h c_j, with c the normed latent
+    [rank] and r the rotated key part [rot] shared by all heads. Only [c | r] is cached (``k_cache`` [nb, bs,
+    rank + rot]; there is no value cache). The up-projections are absorbed: the query is moved into latent space
+    (q_h^plain W_uk,h, one batched product), attention runs as ONE kv head of key size rank + rot whose values are
+    the first ``rank`` columns of the same rows, and W_uv,h is applied to the attended latent."""
+
+    def __init__(self, num_heads: int, dim: int, rot: int, vdim: int, rank: int, scale: float, window: int = 0):
+        super().__init__()
+        self.num_heads, self.dim, self.rot, self.vdim, self.rank = num_heads, dim, rot, vdim, rank
+        self.scale, self.window = float(scale), int(window)
+        self.w_uk = nn.Parameter(torch.empty(num_heads, dim, rank))       # [h, d, r]: rows of W_uk per head
+        self.w_uv = nn.Parameter(torch.empty(num_heads, vdim, rank))
+        self.w_uk.weight_loader = self._load_heads
+        self.w_uv.weight_loader = self._load_heads
+        self.k_cache = torch.tensor([])
+        self.v_cache = torch.tensor([])
+        self.layer_id = -1
+
+    @staticmethod
+    def _load_heads(param, loaded):
+        param.data.copy_(loaded.view(param.shape))
+
+    def cache_rows(self) -> tuple[int, int]:
+        return self.rank + self.rot, 0
+
+    def forward(self, q_plain: torch.Tensor, q_rot_writer, kc: torch.Tensor) -> torch.Tensor:
+        """q_plain [T, H, dim] (a view); q_rot_writer(out_view [T, H, rot]) fills the rotated query part; kc
+        [T, rank + rot] this step's cache rows (used when no cache is bound). Returns [T, H * vdim]."""
+        ctx = get_context()
+        T, H, R = q_plain.shape[0], self.num_heads, self.rank
+        qx = torch.empty(T, H, R + self.rot, dtype=q_plain.dtype, device=q_plain.device)
+        qx[:, :, :R].copy_(torch.bmm(q_plain.transpose(0, 1), self.w_uk).transpose(0, 1))
+        q_rot_writer(qx[:, :, R:])
+        spans = ops.StepSpans.of(ctx)
+        paged = self.k_cache.numel() > 0 and ctx.block_tables is not None
+        if paged:
+            lat = ops.attn_generic(qx, self.k_cache, None, spans, self.scale, 1, R, block_tables=ctx.block_tables,
+                                   window=self.window)
+        else:
+            lat = ops.attn_generic(qx, kc.unsqueeze(1), None, spans, self.scale, 1, R, window=self.window)
+        out = torch.bmm(lat.view(T, H, R).transpose(0, 1), self.w_uv.transpose(1, 2))      # [H, T, vdim]
+        return out.transpose(0, 1).reshape(T, H * self.vdim)
+
+
+class StreamResidual(nn.Module):
+    """Mixing weights of one sublayer of a residual kept in ``streams`` copies: the sublayer reads
+    u = sum_s read[s] x_s and every stream becomes x_t <- sum_s mix[s, t] x_s + write[t] y. The arithmetic runs in
+    ops.stream_mix_norm_, fused with the norm of the next sublayer."""
+
+    def __init__(self, streams: int):
+        super().__init__()
+        self.read, self.write = small_param(streams, fill=1.0), small_param(streams, fill=1.0)
+        self.mix = nn.Parameter(torch.eye(streams, dtype=F32))

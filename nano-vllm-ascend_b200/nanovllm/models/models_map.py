@@ -3,7 +3,8 @@
 The dense families of the hot-path scope and the Qwen3-MoE stack (SURVEY.md 8 f4) are registered;
 the reference's registry (models/models_map.py) also lists its MiniCPM and vision-language stacks,
 which this build deliberately leaves out. Zegopel (a hybrid of softmax attention, lightning attention and
-Mamba-2 layers) is an addition; its config.json names it with an ``"architecture"`` string (config.NativeConfig). Qwen2 checkpoints are served by the Qwen3 class, as in the reference:
+Mamba-2 layers) and Nirelix (retention, gated delta rule and latent attention on a residual kept in several
+streams) are additions; their config.json names them with an ``"architecture"`` string (config.NativeConfig). Qwen2 checkpoints are served by the Qwen3 class, as in the reference:
 the config's ``attention_bias`` decides between QKV bias (Qwen2) and QK-norm (Qwen3).
 """
 from __future__ import annotations
@@ -11,6 +12,7 @@ from __future__ import annotations
 from .llama import LlamaForCausalLM
 from .qwen3 import Qwen3ForCausalLM
 from .qwen3_moe import Qwen3MoeForCausalLM
+from .nirelix import NirelixForCausalLM
 from .zegopel import ZegopelForCausalLM
 
 model_dict: dict[str, type] = {}
@@ -24,5 +26,6 @@ for _arch, _cls in (("Qwen3ForCausalLM", Qwen3ForCausalLM),
                     ("Qwen2ForCausalLM", Qwen3ForCausalLM),
                     ("Qwen3MoeForCausalLM", Qwen3MoeForCausalLM),
                     ("LlamaForCausalLM", LlamaForCausalLM),
-                    ("Zegopel", ZegopelForCausalLM)):
+                    ("Zegopel", ZegopelForCausalLM),
+                    ("Nirelix", NirelixForCausalLM)):
     register(_arch, _cls)

@@ -710,10 +710,11 @@ def act_and_mul(x, act="silu"):
     return out
 
 
-def attn_generic(q, k, v, spans: StepSpans, scale, num_kv_heads, vdim, block_tables=None):
+def attn_generic(q, k, v, spans: StepSpans, scale, num_kv_heads, vdim, block_tables=None, window=0):
     """Causal softmax attention for any head sizes and dtypes. q [T, H, dim]; packed mode: k [Tk, G, dim],
     v [Tk, G, vdim] (token-strided views allowed) in the order of spans.cu_k; paged mode (block_tables given):
-    k, v are the caches [nb, bs, G*dim], [nb, bs, G*vdim]. Returns [T, H*vdim]."""
+    k, v are the caches [nb, bs, G*dim], [nb, bs, G*vdim]. Returns [T, H*vdim]. window > 0: position i sees the
+    keys j with 0 <= i - j < window. v None: the values are the first vdim columns of the key rows."""
     _need_cuda(q, k, v, block_tables)
     T, H, dim = q.shape
     if q.stride(2) != 1 or q.stride(1) != dim:
@@ -723,20 +724,23 @@ def attn_generic(q, k, v, spans: StepSpans, scale, num_kv_heads, vdim, block_tab
         if block_tables.dtype != torch.int32 or block_tables.stride(1) != 1:
             raise TypeError("block_tables must be row-major int32")
         _, bs = _cache_dims(k, G * dim)
-        _cache_dims(v, G * vdim)
+        if v is not None:
+            _cache_dims(v, G * vdim)
         ks, vs, bt_ptr, bt_stride = G * dim, G * vdim, block_tables.data_ptr(), block_tables.stride(0)
     else:
-        if k.stride(2) != 1 or k.stride(1) != dim or v.stride(2) != 1 or v.stride(1) != vdim:
+        if k.stride(2) != 1 or k.stride(1) != dim or (v is not None and (v.stride(2) != 1 or v.stride(1) != vdim)):
             raise ValueError("k/v must be contiguous in (heads, dim)")
         bs, bt_ptr, bt_stride = 0, None, 0
         ks = k.stride(0) if k.shape[0] > 1 else G * dim
-        vs = v.stride(0) if v.shape[0] > 1 else G * vdim
+        vs = (v.stride(0) if v.shape[0] > 1 else G * vdim) if v is not None else 0
+    if v is None and (G != 1 and vdim != dim or vdim > dim):
+        raise ValueError("values inside the key rows: one kv head with vdim <= dim, or vdim == dim")
     out = torch.empty(T, H * vdim, dtype=q.dtype, device=q.device)
     cu_q, cu_k, ctx = spans.ptrs()
     _C.check(_C.load().b200_attn_generic(out.data_ptr(), q.data_ptr(), q.stride(0) if T > 1 else H * dim,
-                                         k.data_ptr(), ks, v.data_ptr(), vs, bt_ptr, bt_stride, bs, cu_q, cu_k, ctx,
-                                         spans.num_seqs, spans.max_q, H, G, dim, vdim, float(scale), _dt3(q),
-                                         _stream()), "b200_attn_generic")
+                                         k.data_ptr(), ks, _ptr(v), vs, bt_ptr, bt_stride, bs, cu_q, cu_k, ctx,
+                                         spans.num_seqs, spans.max_q, H, G, dim, vdim, float(scale), int(window),
+                                         _dt3(q), _stream()), "b200_attn_generic")
     return out
 
 
@@ -751,9 +755,12 @@ def linear_recurrence(q, k, v, spans: StepSpans, num_heads, groups, kdim, vdim, 
     _need_cuda(q, k, v, state, state_slots, decay, dt, dt_bias, a_log, d_skip)
     _f32(decay, dt_bias, a_log, d_skip, state)
     T = q.shape[0]
+    qk_f32 = q.dtype == torch.float32 and v.dtype != torch.float32     # q, k rotated or normalised in fp32 upstream
     for t, n in ((q, groups * kdim), (k, groups * kdim), (v, num_heads * vdim)):
-        if t.dim() != 2 or t.shape[1] != n or t.stride(1) != 1 or t.dtype != q.dtype:
+        if t.dim() != 2 or t.shape[1] != n or t.stride(1) != 1 or (t.dtype != q.dtype and not (qk_f32 and t is v)):
             raise ValueError("q, k [T, groups*kdim] and v [T, H*vdim] with unit inner stride, one dtype")
+    if qk_f32 and (decay is None or act_silu):
+        raise ValueError("fp32 q/k beside 16-bit v: constant-decay form without activation only")
     if state is not None and tuple(state.shape[1:]) != (num_heads, kdim, vdim):
         raise ValueError(f"state must be [slots, {num_heads}, {kdim}, {vdim}]")
     if state is not None and (state_slots is None or state_slots.dtype != torch.int32):
@@ -768,5 +775,188 @@ def linear_recurrence(q, k, v, spans: StepSpans, num_heads, groups, kdim, vdim, 
         out.data_ptr(), q.data_ptr(), stride(q), k.data_ptr(), stride(k), v.data_ptr(), stride(v), _ptr(state),
         _ptr(state_slots), cu_q, cu_k, ctx, spans.num_seqs, spans.max_q, num_heads, groups, kdim, vdim, mode,
         1 if act_silu else 0, _ptr(decay), _ptr(dt), stride(dt) if dt is not None else 0, _ptr(dt_bias),
-        _ptr(a_log), _ptr(d_skip), _dt3(q), _stream()), "b200_linear_recurrence")
+        _ptr(a_log), _ptr(d_skip), 1 if qk_f32 else 0, _dt3(v), _stream()), "b200_linear_recurrence")
+    return out
+
+
+# ---------------------------------------------------------------------------------------------------
+# Multi-stream residuals, rotary positions, delta rule, latent attention, clamped gated unit (csrc/stream_ops.cu,
+# csrc/delta_rule.cu) and the generic mixture-of-experts kernels (csrc/moe_generic.cu).
+def stream_mix_norm_(x, y, mix, out_w, in_w, w, b, eps, dtype, kind="layer", offset=0.0, sum_out=False):
+    """x fp32 [rows, S, hidden] (in place). With y [rows, hidden]: every stream t becomes sum_s mix[s, t] x_s +
+    out_w[t] y. Then u = sum_t in_w[t] x_t (in_w None: the plain sum) and h = norm(u) in `dtype` when w is given:
+    kind "layer" (u - mean) / sqrt(var + eps) * w + b, kind "rms" u / sqrt(mean u^2 + eps) * (offset + w).
+    Returns h (or None), and u as fp32 too when sum_out."""
+    _need_cuda(x, y, mix, out_w, in_w, w, b)
+    _f32(x, mix, out_w, in_w, w, b)
+    rows, S, hidden = x.shape
+    if y is not None and (not y.is_contiguous() or y.shape != (rows, hidden) or y.dtype != dtype):
+        raise ValueError("y must be a contiguous [rows, hidden] tensor of the model dtype")
+    h = torch.empty(rows, hidden, dtype=dtype, device=x.device) if w is not None else None
+    u = torch.empty(rows, hidden, dtype=torch.float32, device=x.device) if sum_out else None
+    _C.check(_C.load().b200_stream_mix_norm(_ptr(h), x.data_ptr(), _ptr(y), _ptr(mix), _ptr(out_w), _ptr(in_w),
+                                            _ptr(w), _ptr(b), _ptr(u), float(eps), float(offset),
+                                            {"layer": 0, "rms": 1}[kind], rows, S, hidden, _DT3[dtype], _stream()),
+             "b200_stream_mix_norm")
+    return (h, u) if sum_out else h
+
+
+def rotary_heads(x, positions, heads, width, dims, base, interleaved, out=None, out_f32=False, split=0,
+                 scale_lo=1.0, scale_hi=1.0):
+    """x [T, heads, width] (a strided view: unit inner stride, any head and token strides). The first `dims` columns
+    of every head are rotated by pos * base^(-2i/dims) in pairs (2i, 2i+1) (interleaved) or (i, i + dims/2); heads
+    below `split` are then multiplied by scale_lo, the others by scale_hi. out: a view of the same shape (fp32 when
+    out_f32, else x's dtype); by default a new contiguous tensor."""
+    _need_cuda(x, positions, out)
+    T = x.shape[0]
+    if x.dim() != 3 or x.shape[1:] != (heads, width) or x.stride(2) != 1:
+        raise ValueError("x must be [T, heads, width] with unit inner stride")
+    if positions.dtype != torch.int64 or not positions.is_contiguous():
+        raise TypeError("positions must be contiguous int64")
+    if out is None:
+        out = torch.empty(T, heads, width, dtype=torch.float32 if out_f32 else x.dtype, device=x.device)
+    if out.shape != x.shape or out.stride(2) != 1 or out.dtype != (torch.float32 if out_f32 else x.dtype):
+        raise ValueError("out must be shaped like x, unit inner stride, fp32 or x's dtype")
+    _C.check(_C.load().b200_rotary_heads(out.data_ptr(), out.stride(0) if T > 1 else 0, out.stride(1),
+                                         1 if out_f32 else 0, x.data_ptr(), x.stride(0) if T > 1 else 0, x.stride(1),
+                                         positions.data_ptr(), T, heads, width, int(dims), float(base),
+                                         1 if interleaved else 0, int(split), float(scale_lo), float(scale_hi),
+                                         _dt3(x), _stream()), "b200_rotary_heads")
+    return out
+
+
+def delta_prep(qk, a, b, dt_bias, a_log, num_heads, groups, dim, unit_eps, q_scale):
+    """qk [T, 2*groups*dim] (q heads then k heads), a [T, H*dim], b [T, H] (row-strided views allowed) ->
+    (qk fp32 unit vectors with q scaled, decay fp32 [T, H*dim], beta fp32 [T, H])."""
+    _need_cuda(qk, a, b, dt_bias, a_log)
+    _f32(dt_bias, a_log)
+    T = qk.shape[0]
+    if qk.shape[1] != 2 * groups * dim or a.shape != (T, num_heads * dim) or b.shape != (T, num_heads):
+        raise ValueError("delta_prep shapes")
+    if qk.stride(1) != 1 or a.stride(1) != 1 or b.stride(1) != 1 or a.dtype != qk.dtype or b.dtype != qk.dtype:
+        raise ValueError("delta_prep inputs: unit inner stride, one dtype")
+    dev = qk.device
+    qk32 = torch.empty(T, 2 * groups * dim, dtype=torch.float32, device=dev)
+    decay = torch.empty(T, num_heads * dim, dtype=torch.float32, device=dev)
+    beta = torch.empty(T, num_heads, dtype=torch.float32, device=dev)
+    stride = lambda t: t.stride(0) if T > 1 else t.shape[1]
+    _C.check(_C.load().b200_delta_prep(qk32.data_ptr(), decay.data_ptr(), beta.data_ptr(), qk.data_ptr(), stride(qk),
+                                       a.data_ptr(), stride(a), b.data_ptr(), stride(b), dt_bias.data_ptr(),
+                                       a_log.data_ptr(), T, num_heads, groups, dim, float(unit_eps), float(q_scale),
+                                       _dt3(qk), _stream()), "b200_delta_prep")
+    return qk32, decay, beta
+
+
+def delta_rule(q, k, v, g, beta, spans: StepSpans, num_heads, groups, kdim, vdim, state=None, state_slots=None):
+    """Gated delta rule per head (S fp32 [kdim, vdim], carried in state[slot]): S <- diag(g) S; w = beta (v - S^T k);
+    S <- S + k w^T; o = S^T q. q, k fp32 [T, groups*kdim] (row-strided views allowed), g fp32 [T, H*kdim], beta fp32
+    [T, H], v [T, H*vdim] in the model dtype. Returns fp32 [T, H*vdim]."""
+    _need_cuda(q, k, v, g, beta, state, state_slots)
+    _f32(g, beta, state)
+    T = q.shape[0]
+    for t, n in ((q, groups * kdim), (k, groups * kdim)):
+        if t.dtype != torch.float32 or t.shape != (T, n) or t.stride(1) != 1:
+            raise ValueError("q, k fp32 [T, groups*kdim] with unit inner stride")
+    if v.shape != (T, num_heads * vdim) or v.stride(1) != 1 or g.shape != (T, num_heads * kdim) or \
+            beta.shape != (T, num_heads):
+        raise ValueError("delta_rule shapes")
+    if state is not None and tuple(state.shape[1:]) != (num_heads, kdim, vdim):
+        raise ValueError(f"state must be [slots, {num_heads}, {kdim}, {vdim}]")
+    if state is not None and (state_slots is None or state_slots.dtype != torch.int32):
+        raise TypeError("state_slots must be int32")
+    out = torch.empty(T, num_heads * vdim, dtype=torch.float32, device=q.device)
+    cu_q, cu_k, ctx = spans.ptrs()
+    stride = lambda t: t.stride(0) if T > 1 else t.shape[1]
+    _C.check(_C.load().b200_delta_rule(out.data_ptr(), q.data_ptr(), stride(q), k.data_ptr(), stride(k), v.data_ptr(),
+                                       stride(v), g.data_ptr(), beta.data_ptr(), _ptr(state), _ptr(state_slots),
+                                       cu_q, cu_k, ctx, spans.num_seqs, num_heads, groups, kdim, vdim, _dt3(v),
+                                       _stream()), "b200_delta_rule")
+    return out
+
+
+def latent_kv_prep(dq, dkv, wq, wc, positions, rank, rot, dims, base, interleaved, eps, cache=None, slots=None):
+    """dq [T, q_rank], dkv [T, rank + rot] (row-strided views) -> (cq [T, q_rank] = rms(dq) * wq, kc [T, rank + rot] =
+    [rms(dkv[:, :rank]) * wc | rotary(dkv[:, rank:])]); kc rows are also stored at `slots` of the paged cache
+    [nb, bs, rank + rot] when given."""
+    _need_cuda(dq, dkv, wq, wc, positions, cache, slots)
+    _f32(wq, wc)
+    T, q_rank = dq.shape
+    if dkv.shape != (T, rank + rot) or dq.stride(1) != 1 or dkv.stride(1) != 1 or dq.dtype != dkv.dtype:
+        raise ValueError("latent_kv_prep shapes")
+    if positions.dtype != torch.int64 or not positions.is_contiguous():
+        raise TypeError("positions must be contiguous int64")
+    have = cache is not None and cache.numel() > 0 and slots is not None
+    bs = 0
+    if have:
+        _, bs = _cache_dims(cache, rank + rot)
+        if slots.dtype != torch.int32 or not slots.is_contiguous() or cache.dtype != dq.dtype:
+            raise TypeError("slots contiguous int32; cache of the activations' dtype")
+    cq = torch.empty(T, q_rank, dtype=dq.dtype, device=dq.device)
+    kc = torch.empty(T, rank + rot, dtype=dq.dtype, device=dq.device)
+    stride = lambda t: t.stride(0) if T > 1 else t.shape[1]
+    _C.check(_C.load().b200_latent_kv_prep(cq.data_ptr(), kc.data_ptr(), cache.data_ptr() if have else None,
+                                           slots.data_ptr() if have else None,
+                                           1 if (have and slots.dim() == 2) else 0, bs, dq.data_ptr(), stride(dq),
+                                           dkv.data_ptr(), stride(dkv), wq.data_ptr(), wc.data_ptr(),
+                                           positions.data_ptr(), T, q_rank, rank, rot, int(dims), float(base),
+                                           1 if interleaved else 0, float(eps), _dt3(dq), _stream()),
+             "b200_latent_kv_prep")
+    return cq, kc
+
+
+def glu_clamped(x, alpha, limit):
+    """x [rows, 2*inter] = (gate | up) -> g sigmoid(alpha g) (u + 1) with g = min(gate, limit), u = clamp(up, +-limit)."""
+    _need_cuda(x)
+    if not x.is_contiguous() or x.dim() != 2:
+        raise ValueError("glu_clamped input must be a contiguous matrix")
+    rows, inter = x.shape[0], x.shape[1] // 2
+    out = torch.empty(rows, inter, dtype=x.dtype, device=x.device)
+    _C.check(_C.load().b200_glu_clamped(out.data_ptr(), x.data_ptr(), rows, inter, float(alpha), float(limit),
+                                        _dt3(x), _stream()), "b200_glu_clamped")
+    return out
+
+
+def moe_route_grouped(router_logits, bias, top_k, groups=1, keep=1, scale=1.0):
+    """Sigmoid router with a selection bias and group-limited choice. router_logits fp32 [T, E]; bias fp32 [E] or
+    None -> (topk_ids int32 [T, k], topk_weights fp32 [T, k])."""
+    _need_cuda(router_logits, bias)
+    _f32(bias)
+    if router_logits.dtype != torch.float32 or router_logits.stride(1) != 1:
+        raise TypeError("router logits are fp32 with unit inner stride")
+    T, E = router_logits.shape
+    ids = torch.empty(T, top_k, dtype=torch.int32, device=router_logits.device)
+    w = torch.empty(T, top_k, dtype=torch.float32, device=router_logits.device)
+    _C.check(_C.load().b200_moe_route_grouped(ids.data_ptr(), w.data_ptr(), router_logits.data_ptr(),
+                                              router_logits.stride(0) if T > 1 else E, _ptr(bias), T, E, int(top_k),
+                                              int(groups), int(keep), float(scale), _stream()),
+             "b200_moe_route_grouped")
+    return ids, w
+
+
+def moe_experts_generic(x, w13, w2, topk_weights, plan: MoePlan) -> torch.Tensor:
+    """Expert MLPs down(silu(gate x) * up x) and the weighted combine for any sizes and dtypes (fp32 included):
+    x [T, hidden]; w13 [E, 2*inter, hidden]; w2 [E, hidden, inter]; topk_weights fp32 [T, k]."""
+    _need_cuda(x, w13, w2, topk_weights)
+    _f32(topk_weights)
+    T, hidden = x.shape
+    E, two_i, _ = w13.shape
+    inter, k = two_i // 2, plan.top_k
+    if w13.shape != (E, 2 * inter, hidden) or w2.shape != (E, hidden, inter) or E != plan.num_local:
+        raise ValueError("expert weight shapes do not match")
+    if not (w13.is_contiguous() and w2.is_contiguous()) or x.stride(1) != 1 or x.dtype != w13.dtype or x.dtype != w2.dtype:
+        raise ValueError("contiguous expert weights of x's dtype; x row-major")
+    pairs = T * k
+    lib = _C.load()
+    h = torch.empty(pairs, inter, dtype=x.dtype, device=x.device)
+    y = torch.empty(pairs, hidden, dtype=torch.float32, device=x.device)
+    out = torch.empty(T, hidden, dtype=x.dtype, device=x.device)
+    _C.check(lib.b200_moe_gemm_generic(h.data_ptr(), x.data_ptr(), x.stride(0) if T > 1 else hidden, w13.data_ptr(),
+                                       plan.offsets.data_ptr(), plan.sorted_pair.data_ptr(), pairs, hidden, inter, E,
+                                       k, 1, _dt3(x), _stream()), "b200_moe_gemm_generic (gate_up)")
+    _C.check(lib.b200_moe_gemm_generic(y.data_ptr(), h.data_ptr(), inter, w2.data_ptr(), plan.offsets.data_ptr(),
+                                       plan.sorted_pair.data_ptr(), pairs, inter, hidden, E, k, 0, _dt3(x),
+                                       _stream()), "b200_moe_gemm_generic (down)")
+    _C.check(lib.b200_moe_combine_weighted(out.data_ptr(), y.data_ptr(), topk_weights.data_ptr(),
+                                           plan.pos_of_pair.data_ptr(), T, k, hidden, _dt3(x), _stream()),
+             "b200_moe_combine_weighted")
     return out

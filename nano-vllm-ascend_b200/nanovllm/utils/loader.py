@@ -50,6 +50,17 @@ def load_model(model: nn.Module, path: str) -> int:
     return count
 
 
+def checkpoint_shapes(path: str) -> dict[str, tuple[int, ...]]:
+    """{tensor name: shape} of every *.safetensors under `path`, from the headers alone."""
+    from safetensors import safe_open
+    shapes = {}
+    for file in sorted(glob(os.path.join(path, "*.safetensors"))):
+        with safe_open(file, "pt", "cpu") as f:
+            for name in f.keys():
+                shapes[name] = tuple(f.get_slice(name).get_shape())
+    return shapes
+
+
 def full_shapes(model: nn.Module, tp_size: int) -> dict[str, tuple[int, ...]]:
     """Unsharded shape of every parameter (what a checkpoint would hold)."""
     shapes = {}
