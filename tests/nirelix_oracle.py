@@ -136,7 +136,7 @@ def latent_attention_mixer(u, P, m, eps):
     kn = (c @ P["uk"].T).view(T, H, d)
     val = (c @ P["uv"].T).view(T, H, dv)
     out = torch.zeros(T, H, dv, dtype=u.dtype)
-    W = m["mask"]["size"]
+    W = (m.get("mask") or {}).get("size") or T + 1          # no mask entry: plain causal attention
     for i in range(T):
         lo = max(0, i - W + 1)
         for h in range(H):
@@ -160,7 +160,8 @@ def route(z, correction, r):
     T, E = z.shape
     s = torch.sigmoid(z)
     choice = s + correction
-    n, keep, top = r["groups"]["count"], r["groups"]["keep"], r["top"]
+    grp_cfg = r.get("groups") or {"count": 1, "keep": 1}
+    n, keep, top = grp_cfg["count"], grp_cfg["keep"], r["top"]
     per = E // n
     grp = choice.view(T, n, per)
     gscore = grp.topk(min(2, per), -1).values.sum(-1)
@@ -171,7 +172,7 @@ def route(z, correction, r):
                          torch.full_like(choice, -math.inf))
     idx = masked.topk(top, -1).indices
     w = s.gather(1, idx)
-    w = w / (w.sum(-1, keepdim=True) + 1e-20) * r["scale"]
+    w = w / (w.sum(-1, keepdim=True) + 1e-20) * r.get("scale", 1.0)
     return idx, w
 
 
@@ -223,3 +224,79 @@ def forward(config, tensors, tokens, return_layers=False):
     h = layer_norm(X.sum(0), tensors["final.norm"], tensors["final.norm.b"], eps)
     logits = h @ tensors["head"].T
     return (logits, torch.stack(layers)) if return_layers else logits
+
+
+def random_model(config, seed=0, ranks=(5, 3)):
+    """Random bf16-representable weights for `config` under the checkpoint's names and shapes, returned as
+    {name: bf16 tensor}. `ranks`: inner sizes of the delta mixers' low-rank decay and gate projections."""
+    g = torch.Generator().manual_seed(seed)
+    W, V, S = config["width"], config["vocab"], config.get("streams")
+    t = {}
+
+    def mat(name, out, inn, s=None):
+        t[name] = (torch.randn(out, inn, generator=g) * (s if s is not None else inn ** -0.5)).bfloat16()
+
+    def vec(name, n, s=0.1, mean=0.0):
+        t[name] = (mean + torch.randn(n, generator=g) * s).bfloat16()
+
+    mat("embed", V, W, 1.0)
+    for i, layer in enumerate(config["layers"]):
+        p, m = f"l{i}.", layer["mixer"]
+        for q in ("1", "2") if layer.get("mlp") else ("1",):
+            vec(p + "norm" + q, W, mean=1.0)
+            vec(p + "norm" + q + ".b", W)
+            if S is not None:
+                vec(p + f"hc{q}.in", S, 0.2, S ** -0.5)
+                vec(p + f"hc{q}.out", S, 0.2, 1.0)
+                t[p + f"hc{q}.mix"] = (torch.eye(S) + 0.15 * torch.randn(S, S, generator=g)).bfloat16()
+        if layer["type"] == "retention":
+            H, d, dv = m["heads"], m["dim"], m["vdim"]
+            for n, rows in (("q", H * d), ("k", H * d), ("v", H * dv), ("g", H * dv)):
+                mat(p + "mix." + n, rows, W)
+            mat(p + "mix.o", W, H * dv)
+        elif layer["type"] == "channel_delta":
+            H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            for n, rows in (("q", G * d), ("k", G * d), ("v", H * dv)):
+                mat(p + "mix." + n, rows, W)
+                t[p + "mix." + n + ".conv"] = (torch.randn(rows, m["conv"], generator=g) * 0.5).bfloat16()
+            mat(p + "mix.b", H, W)
+            t[p + "mix.A_log"] = (torch.rand(H, generator=g) * 3 - 4).bfloat16()
+            vec(p + "mix.norm", dv, mean=1.0)
+            mat(p + "mix.a1", ranks[0], W)
+            mat(p + "mix.a2", H * d, ranks[0], 1.0)
+            vec(p + "mix.dt_bias", H * d, 1.0)
+            mat(p + "mix.g1", ranks[1], W)
+            mat(p + "mix.g2", H * dv, ranks[1], 1.0)
+            mat(p + "mix.o", W, H * dv)
+        else:
+            H, d, dr, dv, R, Q = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["q_rank"]
+            mat(p + "mix.dq", Q, W)
+            vec(p + "mix.dq.norm", Q, mean=1.0)
+            mat(p + "mix.uq", H * (d + dr), Q)
+            mat(p + "mix.dkv", R + dr, W)
+            vec(p + "mix.dkv.norm", R, mean=1.0)
+            mat(p + "mix.uk", H * d, R)
+            mat(p + "mix.uv", H * dv, R)
+            mat(p + "mix.g", H * dv, W)
+            mat(p + "mix.o", W, H * dv)
+        mlp = layer.get("mlp")
+        if mlp and mlp["kind"] == "dense":
+            mat(p + "mlp.gate", mlp["ff"], W, 2.0 * W ** -0.5)
+            mat(p + "mlp.up", mlp["ff"], W, 2.0 * W ** -0.5)
+            mat(p + "mlp.down", W, mlp["ff"])
+        elif mlp:
+            E, ff = mlp["router"]["experts"], mlp["expert"]["ff"]
+            for e in range(E):
+                mat(p + f"mlp.e{e}.gate", ff, W)
+                mat(p + f"mlp.e{e}.up", ff, W)
+                mat(p + f"mlp.e{e}.down", W, ff)
+            mat(p + "mlp.router", E, W, 2.0 * W ** -0.5)
+            vec(p + "mlp.correction", E, 0.5, -0.3)
+    vec("final.norm", W, mean=1.0)
+    vec("final.norm.b", W)
+    mat("head", V, W)
+    return t
+
+
+def as_f64(tensors):
+    return {k: v.to(F64) for k, v in tensors.items()}
