@@ -23,7 +23,8 @@ the all-reduce form and its latency, and the same workload at TP=1 (rank 0) for 
 `--tp` instead makes the tensor-parallel engine the whole line ("strong" scaling).
 `--impl reference` times only the CPU reference arm.
 `--hybrid` leaves the contract workload aside: the Zegopel hybrid decoder beside the dense decoder of the same width
-(prefill and decode throughput through the engine) and the rooflines of its kernels beside their like kernels.
+(prefill and decode throughput through the engine) and the rooflines of its kernels beside their like kernels;
+`--hybrid --design nirelix` does the same for the Nirelix decoder beside the Zegopel decoder of the same width.
 """
 from __future__ import annotations
 
@@ -107,7 +108,11 @@ def parse_args():
     ap.add_argument("--hybrid", action="store_true",
                     help="instead of the contract workload: prefill and decode throughput of the Zegopel hybrid "
                          "decoder beside the dense decoder of the same width and depth, and its kernels' rooflines")
-    ap.add_argument("--hybrid-pairs", default="zegopel-1k:qwen3-0.6b,zegopel-2k:llama-3.2-1b")
+    ap.add_argument("--hybrid-pairs", default=None,
+                    help="model:model,... (default zegopel-1k:qwen3-0.6b,zegopel-2k:llama-3.2-1b; with --design "
+                         "nirelix: nirelix-1k:zegopel-1k,nirelix-2k:zegopel-2k)")
+    ap.add_argument("--design", default="zegopel", choices=["zegopel", "nirelix"],
+                    help="with --hybrid: whose presets and kernel table are measured")
     ap.add_argument("--kv-cache-dtype", default="auto", choices=["auto", "fp8"],
                     help="fp8: e4m3 KV cache (an extra line; the contract line is the default bf16 cache)")
     return ap.parse_args()
@@ -711,6 +716,135 @@ def hybrid_kernel_table(width, head_dim, tokens, seqs, peak_gbs):
     return rows
 
 
+def nirelix_kernel_table(width, head_dim, tokens, seqs, peak_gbs):
+    """The kernels that the Nirelix decoder adds, alone, at the layer sizes of a `width`-wide model, as a prompt step
+    (`seqs` x tokens/seqs) and as a decode step (`seqs` rows at that context), each beside the like kernel of the
+    Zegopel decoder. frac = algorithmic bytes / time / measured copy bandwidth."""
+    from nanovllm import ops
+    dev, bf = "cuda", torch.bfloat16
+    g = torch.Generator(device=dev).manual_seed(0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    rnd = lambda *shape: torch.randn(*shape, device=dev, generator=g)
+    H = width // head_dim
+    G = max(1, H // 2)
+    S = 4
+    rows = []
+
+    def add(name, step, fn, nbytes, like=None, like_fn=None, like_bytes=None, flops=None):
+        t = _timed(fn, flush)
+        row = {"kernel": name, "step": step, "us": round(t * 1e6, 1), "GB/s": round(nbytes / t / 1e9),
+               "frac_of_measured_copy": round(nbytes / t / 1e9 / peak_gbs, 3)}
+        if flops:
+            row["TFLOP/s"] = round(flops / t / 1e12, 2)
+        if like_fn is not None:
+            tl = _timed(like_fn, flush)
+            row["like"] = {"kernel": like, "us": round(tl * 1e6, 1),
+                           "frac_of_measured_copy": round(like_bytes / tl / 1e9 / peak_gbs, 3)}
+            row["times_as_far_from_roofline_as_like"] = round((like_bytes / tl) / (nbytes / t), 2)
+        rows.append(row)
+
+    for step, T in (("prompt", tokens), ("decode", seqs)):
+        per = T // seqs if step == "prompt" else 1
+        ctx = tokens // seqs
+        if step == "prompt":
+            cu = torch.arange(0, T + 1, per, dtype=torch.int32, device=dev)
+            spans = ops.StepSpans(cu, cu, None, per)
+        else:
+            spans = ops.StepSpans(None, None, torch.full((T,), ctx, dtype=torch.int32, device=dev))
+        slots = torch.arange(seqs, dtype=torch.int32, device=dev)
+        pos = (torch.arange(T, device=dev) % max(per, 1) + (0 if step == "prompt" else ctx - 1)).contiguous()
+        # residual path: S streams rewritten + read + layer norm, beside the one-stream add + two RMS norms
+        X, y, res = rnd(T, S, width), rnd(T, width).to(bf), rnd(T, width)
+        mix, ow, iw, w1, w2 = rnd(S, S), rnd(S), rnd(S), rnd(width), rnd(width)
+        add("stream_mix_norm(4 streams)", step,
+            lambda: ops.stream_mix_norm_(X, y, mix, ow, iw, w1, w2, 1e-6, bf), T * width * (S * 8 + 4),
+            "residual_add_norms", lambda: ops.residual_add_norms_(y, res, w1, w2, 1e-6), T * width * 12)
+        ff = 3 * width
+        gu = rnd(T, 2 * ff).to(bf)
+        add("glu_clamped", step, lambda: ops.glu_clamped(gu, 1.702, 7.0), T * ff * 6,
+            "act_and_mul(relu)", lambda: ops.act_and_mul(gu, "relu"), T * ff * 6)
+        # retention: rotary on q|k into fp32, then the constant-decay recurrence on fp32 q, k
+        nq = H * head_dim
+        p4 = rnd(T, 4 * nq).to(bf)
+        qk_view = p4[:, :2 * nq].unflatten(1, (2 * H, head_dim))
+        qkv_like = rnd(T, nq + 2 * G * head_dim).to(bf)
+        nb = (T + 15) // 16 + 1
+        kc = torch.zeros(nb, 16, G * head_dim, dtype=bf, device=dev)
+        vc = torch.zeros(nb, 16, G * head_dim, dtype=bf, device=dev)
+        sl = torch.arange(T, dtype=torch.int32, device=dev)
+        add("rotary_heads(q|k -> fp32)", step,
+            lambda: ops.rotary_heads(qk_view, pos, 2 * H, head_dim, head_dim, 1e6, False, out_f32=True, split=H,
+                                     scale_hi=head_dim ** -0.5), T * 2 * nq * 6,
+            "unitnorm_temp_cache", lambda: ops.unitnorm_temp_cache(qkv_like, pos, 1e-6, 0.1, 1024, H, G, head_dim,
+                                                                   head_dim, kc, vc, sl),
+            T * (2 * (nq + G * head_dim) * 2 + 3 * G * head_dim * 2))
+        qk32 = rnd(T, 2 * nq)
+        decay = torch.linspace(0.9, 0.999, H, device=dev)
+        st = torch.zeros(seqs + 1, H, head_dim, head_dim, device=dev)
+        state_bytes = 2 * seqs * H * head_dim * head_dim * 4 if step == "decode" else 0
+        add("linear_recurrence(fp32 q, k; constant decay)", step,
+            lambda: ops.linear_recurrence(qk32[:, :nq], qk32[:, nq:], p4[:, 2 * nq:3 * nq], spans, H, H, head_dim,
+                                          head_dim, st, slots, decay=decay), T * nq * (2 * 4 + 2 + 4) + state_bytes,
+            "linear_recurrence(bf16 q, k)", lambda: ops.linear_recurrence(p4[:, :nq], p4[:, nq:2 * nq], p4[:, 2 * nq:3 * nq],
+                                                                         spans, H, H, head_dim, head_dim, st, slots,
+                                                                         decay=decay, act_silu=True),
+            T * nq * (3 * 2 + 4) + state_bytes, flops=4.0 * T * H * head_dim * head_dim)
+        # delta rule: preparation, then the recurrence (like: the selective recurrence, which also decays per token)
+        ngk = G * head_dim
+        qkc = rnd(T, 2 * ngk + nq).to(bf)
+        a_in, b_in = rnd(T, nq).to(bf), rnd(T, H).to(bf)
+        dtb, alog = rnd(nq), -torch.rand(H, device=dev, generator=g) * 2 - 1
+        add("delta_prep", step, lambda: ops.delta_prep(qkc[:, :2 * ngk], a_in, b_in, dtb, alog, H, G, head_dim, 1e-6,
+                                                       head_dim ** -0.5), T * (2 * ngk * 6 + nq * 6 + H * 6))
+        q32, dec, beta = ops.delta_prep(qkc[:, :2 * ngk], a_in, b_in, dtb, alog, H, G, head_dim, 1e-6, head_dim ** -0.5)
+        Hm, dvm, N, Gm = 2 * width // 64, 64, 128, 8
+        xbc = rnd(T, Hm * dvm + 2 * Gm * N).to(bf)
+        dt = rnd(T, Hm).to(bf)
+        stm = torch.zeros(seqs + 1, Hm, N, dvm, device=dev)
+        par = [rnd(Hm) * 0.5, -torch.rand(Hm, device=dev, generator=g) * 2, torch.ones(Hm, device=dev)]
+        inner = Hm * dvm
+        add("delta_rule", step,
+            lambda: ops.delta_rule(q32[:, :ngk], q32[:, ngk:], qkc[:, 2 * ngk:], dec, beta, spans, H, G, head_dim,
+                                   head_dim, st, slots), T * (2 * ngk * 4 + nq * 4 + nq * 2 + nq * 4) + state_bytes,
+            "linear_recurrence(selective)",
+            lambda: ops.linear_recurrence(xbc[:, inner + Gm * N:], xbc[:, inner:inner + Gm * N], xbc[:, :inner], spans,
+                                          Hm, Gm, N, dvm, stm, slots, dt=dt, dt_bias=par[0], a_log=par[1], d_skip=par[2]),
+            T * (inner * 6 + 2 * Gm * N * 2) + (2 * seqs * Hm * N * dvm * 4 if step == "decode" else 0),
+            flops=8.0 * T * H * head_dim * head_dim)
+        # latent attention: latent rows + cache write, then attention over [latent | rotated key] rows in a window
+        R, dr, Q, window = 4 * head_dim, head_dim // 2, 3 * width // 4, 512
+        lat = rnd(T, Q + R + dr).to(bf)
+        wq, wc = rnd(Q), rnd(R)
+        nbl = seqs * (-(-ctx // 16)) + 1
+        cache = (torch.randn(nbl, 16, R + dr, device=dev, generator=g) * 0.3).to(bf)
+        tables = torch.arange(seqs * (-(-ctx // 16)), dtype=torch.int32, device=dev).view(seqs, -1)
+        add("latent_kv_prep", step,
+            lambda: ops.latent_kv_prep(lat[:, :Q], lat[:, Q:], wq, wc, pos, R, dr, dr, 1e4, True, 1e-6, cache, sl),
+            T * ((Q + R + dr) * 2 + Q * 2 + 2 * (R + dr) * 2))
+        qx = (rnd(T, H, R + dr) * 0.3).to(bf)
+        keys = min(window, ctx)
+        att_flops = 2.0 * T * H * (min(window, (per + 1) / 2 + 0) if step == "prompt" else keys) * (2 * R + dr)
+        add("attn_generic(latent rows, window 512)", step,
+            lambda: ops.attn_generic(qx, cache, None, spans, 0.07, 1, R, block_tables=tables, window=window),
+            T * H * (R + dr + R) * 2 + seqs * min(ctx, keys + per) * (R + dr) * 2, flops=att_flops)
+        # mixture of experts: router, then the expert kernels (like: the softmax router and the same expert kernels)
+        E, top, ffe = 16, 2, width // 2
+        x = rnd(T, width).to(bf)
+        logits = rnd(T, E)
+        corr = rnd(E) * 0.1
+        add("moe_route_grouped", step, lambda: ops.moe_route_grouped(logits, corr, top, 4, 2, 1.5), T * (E * 4 + top * 8),
+            "moe_route(softmax)", lambda: ops.moe_route(logits.to(bf), top), T * (E * 2 + top * 6))
+        ids, wts = ops.moe_route_grouped(logits, corr, top, 4, 2, 1.5)
+        plan = ops.moe_align(ids, 0, E)
+        w13, w2e = (rnd(E, 2 * ffe, width) * 0.03).to(bf), (rnd(E, width, ffe) * 0.03).to(bf)
+        wb = wts.to(bf)
+        add("moe_experts_generic", step, lambda: ops.moe_experts_generic(x, w13, w2e, wts, plan),
+            3 * E * ffe * width * 2 + T * width * 4,
+            "moe_experts(tensor cores)", lambda: ops.moe_experts(x, w13, w2e, ids, wb, plan),
+            3 * E * ffe * width * 2 + T * width * 4, flops=6.0 * T * top * ffe * width)
+    return rows
+
+
 def hybrid_compare(args):
     """--hybrid: the Zegopel presets beside the dense presets of the same width and depth, each through the engine
     (LLM.add_request / LLM.step; prompt steps, then CUDA-graph decode steps), plus the kernel table."""
@@ -724,7 +858,10 @@ def hybrid_compare(args):
            "dtype": "bf16", "data": "synthetic (random-init weights, random token ids)",
            "config": {"batch": B, "ctx": ctx, "block_size": args.block_size, "l2": "prompts and caches exceed L2; "
                       "kernel table: 256 MB flush before every timed launch"}, "models": [], "peak_source": peak_src}
-    for pair in args.hybrid_pairs.split(","):
+    pairs = args.hybrid_pairs or ("nirelix-1k:zegopel-1k,nirelix-2k:zegopel-2k" if args.design == "nirelix" else
+                                  "zegopel-1k:qwen3-0.6b,zegopel-2k:llama-3.2-1b")
+    out["design"] = args.design
+    for pair in pairs.split(","):
         for name in pair.split(":"):
             llm = LLM(name, kvcache_block_size=args.block_size, max_num_seqs=B, max_model_len=max(4096, ctx + W + K + 16),
                       max_num_batched_tokens=16384, gpu_memory_utilization=args.mem_util, seed=0)
@@ -743,8 +880,9 @@ def hybrid_compare(args):
             release(llm)
             del llm
             torch.cuda.empty_cache()
-    out["kernels"] = {"width_1024_head_128": hybrid_kernel_table(1024, 128, 16384, 16, peak),
-                      "width_2048_head_64": hybrid_kernel_table(2048, 64, 16384, 16, peak)}
+    table = nirelix_kernel_table if args.design == "nirelix" else hybrid_kernel_table
+    out["kernels"] = {"width_1024_head_128": table(1024, 128, 16384, 16, peak),
+                      "width_2048_head_64": table(2048, 64, 16384, 16, peak)}
     out["clocks"] = clocks.stop()
     print(json.dumps(out))
 

@@ -286,9 +286,51 @@ glu_clamped_vec_kernel(T* __restrict__ out, const T* __restrict__ x, int64_t row
   }
 }
 
+// ------------------------------------------------------------------ masked softmax over a block of scores
+// One warp per row of s [rows, nk] (fp32 scores of `heads` query heads per token against keys key_lo .. key_lo + nk - 1
+// of one sequence): row r belongs to the token at position first_pos + r / heads and sees key j iff
+// key_lo + j <= pos and (window == 0 or key_lo + j > pos - window). p = softmax(scale * s) over the visible keys,
+// written in the element type; hidden keys get 0.
+template <typename T>
+__global__ void __launch_bounds__(128)
+masked_softmax_kernel(T* __restrict__ p, const float* __restrict__ s, int64_t rows, int nk, int heads, int first_pos,
+                      int key_lo, int window, float scale) {
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const int pos = first_pos + (int)(r / heads);
+  const int hi = min(nk, pos - key_lo + 1);                                  // visible: [lo, hi)
+  const int lo = window > 0 ? max(0, pos - window + 1 - key_lo) : 0;
+  const float* sr = s + r * nk;
+  T* pr = p + r * nk;
+  float m = -INFINITY;
+  for (int j = lo + lane; j < hi; j += 32) m = fmaxf(m, sr[j]);
+  m = warp_max(m);
+  float l = 0.f;
+  for (int j = lo + lane; j < hi; j += 32) l += expf((sr[j] - m) * scale);
+  l = warp_sum(l);
+  const float inv = l > 0.f ? 1.0f / l : 0.f;
+  for (int j = lane; j < nk; j += 32)
+    pr[j] = from_f32<T>((j >= lo && j < hi) ? expf((sr[j] - m) * scale) * inv : 0.f);
+}
+
 }  // namespace b200
 
 using namespace b200;
+
+extern "C" int b200_masked_softmax(void* p, const float* s, int64_t rows, int32_t nk, int32_t heads,
+                                   int32_t first_pos, int32_t key_lo, int32_t window, float scale, int32_t dtype,
+                                   b200_stream_t stream) {
+  B200_RETURN_IF(rows < 0 || nk <= 0 || heads <= 0 || first_pos < 0 || key_lo < 0 || window < 0 || scale <= 0.f,
+                 B200_ERR_BAD_SHAPE);
+  if (rows == 0) return B200_OK;
+  B200_RETURN_IF(!p || !s, B200_ERR_NULL_POINTER);
+  B200_DISPATCH_3(dtype, T, launch_pdl(masked_softmax_kernel<T>, dim3((unsigned)((rows + 3) / 4)), dim3(128), 0,
+                                       (cudaStream_t)stream, (T*)p, s, rows, nk, heads, first_pos, key_lo, window,
+                                       scale));
+  return finish_launch();
+}
 
 extern "C" int b200_stream_mix_norm(void* h, float* x, const void* y, const float* mix, const float* out_w,
                                     const float* in_w, const float* w, const float* b, float* sum_out,

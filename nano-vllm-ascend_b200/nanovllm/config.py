@@ -65,6 +65,31 @@ def zegopel_preset(width: int, pattern: str, repeats: int, vocab: int = 32768, h
             "layers": [entry[ch] for ch in pattern] * repeats}
 
 
+def nirelix_preset(width: int, pattern: str, repeats: int, vocab: int = 32768, head_dim: int = 128,
+                   streams: int = 4, window: int = 512) -> dict:
+    """A Nirelix configuration of realistic layer sizes for synthetic benchmarks: `pattern` is a string over
+    r (retention), d (channel_delta + mixture of experts) and a (latent_attention + dense feed-forward), repeated
+    `repeats` times."""
+    H = width // head_dim
+    decay = [1.0 - 2.0 ** (-3 - 5 * i / max(1, H - 1)) for i in range(H)]
+    entry = {
+        "r": {"type": "retention", "mlp": None,
+              "mixer": {"heads": H, "dim": head_dim, "vdim": head_dim, "decay": decay,
+                        "rot": {"dims": head_dim, "base": 1e6}}},
+        "d": {"type": "channel_delta",
+              "mlp": {"kind": "moe", "expert": {"ff": width // 2},
+                      "router": {"experts": 16, "top": 2, "groups": {"count": 4, "keep": 2}, "scale": 1.5}},
+              "mixer": {"heads": H, "kv_heads": max(1, H // 2), "dim": head_dim, "vdim": head_dim, "conv": 4,
+                        "decay_rank": 32, "gate_rank": 32}},
+        "a": {"type": "latent_attention", "mlp": {"kind": "dense", "ff": 3 * width, "limit": 7.0},
+              "mixer": {"heads": H, "dim": head_dim, "rot_dim": head_dim // 2, "vdim": head_dim, "kv_rank": 4 * head_dim,
+                        "q_rank": 3 * width // 4, "mask": {"size": window}, "rot": {"dims": head_dim // 2, "base": 1e4},
+                        "scale": (head_dim + head_dim // 2) ** -0.5}},
+    }
+    return {"architecture": "Nirelix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "streams": streams,
+            "layers": [entry[ch] for ch in pattern] * repeats}
+
+
 def preset_hf_config(name: str):
     """Architecture presets built offline from the public model cards."""
     from transformers import LlamaConfig, Qwen3Config, Qwen3MoeConfig
@@ -75,6 +100,12 @@ def preset_hf_config(name: str):
         return NativeConfig(zegopel_preset(2048, "alml", 4, vocab=128256, head_dim=64))
     if key == "tiny-zegopel":
         return NativeConfig(zegopel_preset(128, "alm", 1, vocab=512, head_dim=32))
+    if key == "nirelix-1k":          # 28 layers at width 1024: the size class of zegopel-1k and qwen3-0.6b
+        return NativeConfig(nirelix_preset(1024, "rdardad", 4, vocab=151936))
+    if key == "nirelix-2k":          # 16 layers at width 2048, head size 64: the size class of zegopel-2k
+        return NativeConfig(nirelix_preset(2048, "rdad", 4, vocab=128256, head_dim=64))
+    if key == "tiny-nirelix":
+        return NativeConfig(nirelix_preset(128, "rda", 1, vocab=512, head_dim=32, streams=2, window=24))
     if key == "qwen3-0.6b":
         c = Qwen3Config(vocab_size=151936, hidden_size=1024, num_hidden_layers=28,
                         num_attention_heads=16, num_key_value_heads=8, head_dim=128,

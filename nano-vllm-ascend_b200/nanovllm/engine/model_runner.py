@@ -352,7 +352,8 @@ class ModelRunner:
                     max_seqlen_q=max_q, max_seqlen_k=max_k,
                     slot_mapping=as_dev(slots, torch.int32) if slots is not None else None,
                     context_lens=None, block_tables=block_tables, is_enforce_eager=True,
-                    real_bs=len(seqs), block_size=bs, paged_prefill=hit, state_slots=state_slots)
+                    real_bs=len(seqs), block_size=bs, paged_prefill=hit, state_slots=state_slots,
+                    host_spans=[(cu_q[i], cu_q[i + 1] - cu_q[i], cu_k[i + 1] - cu_k[i]) for i in range(len(seqs))])
         return as_dev(ids, torch.int64), as_dev(pos, torch.int64)
 
     def _dense_block_tables(self, seqs):

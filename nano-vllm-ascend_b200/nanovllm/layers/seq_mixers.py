@@ -215,6 +215,7 @@ class LatentAttention(nn.Module):
         self.k_cache = torch.tensor([])
         self.v_cache = torch.tensor([])
         self.layer_id = -1
+        self.force_generic = False
 
     @staticmethod
     def _load_heads(param, loaded):
@@ -233,13 +234,55 @@ class LatentAttention(nn.Module):
         q_rot_writer(qx[:, :, R:])
         spans = ops.StepSpans.of(ctx)
         paged = self.k_cache.numel() > 0 and ctx.block_tables is not None
-        if paged:
+        if (ctx.is_prefill and ctx.host_spans is not None and qx.dtype != torch.float32 and not self.force_generic
+                and ctx.max_seqlen_q >= self.PRODUCT_MIN_TOKENS):
+            lat = self._prefill_by_products(qx, kc, ctx, paged)
+        elif paged:
             lat = ops.attn_generic(qx, self.k_cache, None, spans, self.scale, 1, R, block_tables=ctx.block_tables,
                                    window=self.window)
         else:
             lat = ops.attn_generic(qx, kc.unsqueeze(1), None, spans, self.scale, 1, R, window=self.window)
         out = torch.bmm(lat.view(T, H, R).transpose(0, 1), self.w_uv.transpose(1, 2))      # [H, T, vdim]
         return out.transpose(0, 1).reshape(T, H * self.vdim)
+
+    PRODUCT_MIN_TOKENS = 64       # longest portion of the step from which prompts run on library products
+    PRODUCT_CHUNK = 512           # query tokens per product
+
+    def _prefill_by_products(self, qx, kc, ctx, paged):
+        """Prompt portions of 16-bit models on the tensor cores: per sequence and per chunk of query tokens, the
+        scores of all heads against the chunk's visible key range as ONE library product with fp32 output (all
+        heads share the latent rows), the masked softmax kernel (fp32 in, 16-bit probabilities out), and one
+        product with the latent part of the same rows. Short portions and fp32 models run on attn_generic."""
+        T, H, R = qx.shape[0], self.num_heads, self.rank
+        D = R + self.rot
+        lat = torch.empty(T, H * R, dtype=qx.dtype, device=qx.device)
+        bs = ctx.block_size
+        flat = self.k_cache.view(-1, D) if paged else None
+        for s, (q0, ql, kl) in enumerate(ctx.host_spans):
+            first = kl - ql
+            if ql < self.PRODUCT_MIN_TOKENS:          # a short portion or a single token beside long ones
+                sub = ops.StepSpans(torch.tensor([0, ql], dtype=torch.int32, device=qx.device),
+                                    torch.tensor([0, kl], dtype=torch.int32, device=qx.device), None, ql)
+                if paged:
+                    lat[q0:q0 + ql] = ops.attn_generic(qx[q0:q0 + ql], self.k_cache, None, sub, self.scale, 1, R,
+                                                       block_tables=ctx.block_tables[s:s + 1], window=self.window)
+                else:
+                    lat[q0:q0 + ql] = ops.attn_generic(qx[q0:q0 + ql], kc[q0:q0 + ql].unsqueeze(1), None, sub,
+                                                       self.scale, 1, R, window=self.window)
+                continue
+            for c0 in range(0, ql, self.PRODUCT_CHUNK):
+                c1 = min(ql, c0 + self.PRODUCT_CHUNK)
+                lo = max(0, first + c0 - self.window + 1) if self.window else 0
+                hi = first + c1
+                if paged:
+                    j = torch.arange(lo, hi, device=qx.device)
+                    rows = flat[ctx.block_tables[s][j // bs].long() * bs + j % bs]
+                else:                                  # no cache bound: the span's keys are this step's rows
+                    rows = kc[q0 + lo:q0 + hi]
+                scores = torch.mm(qx[q0 + c0:q0 + c1].reshape(-1, D), rows.t(), out_dtype=torch.float32)
+                p = ops.masked_softmax(scores, H, first + c0, lo, self.scale, self.window, qx.dtype)
+                lat[q0 + c0:q0 + c1] = torch.mm(p, rows[:, :R]).view(-1, H * R)
+        return lat
 
 
 class StreamResidual(nn.Module):

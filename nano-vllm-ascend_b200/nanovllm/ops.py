@@ -904,6 +904,21 @@ def latent_kv_prep(dq, dkv, wq, wc, positions, rank, rot, dims, base, interleave
     return cq, kc
 
 
+def masked_softmax(scores, heads, first_pos, key_lo, scale, window, dtype):
+    """scores fp32 [rows, nk]: `heads` query heads per token (row r = token first_pos + r // heads) against keys
+    key_lo .. key_lo + nk - 1 of one sequence -> softmax(scale * scores) over the causally visible keys inside the
+    window (0: none), in `dtype`; hidden keys get 0."""
+    _need_cuda(scores)
+    if scores.dtype != torch.float32 or not scores.is_contiguous() or scores.dim() != 2:
+        raise TypeError("scores are a contiguous fp32 matrix")
+    rows, nk = scores.shape
+    p = torch.empty(rows, nk, dtype=dtype, device=scores.device)
+    _C.check(_C.load().b200_masked_softmax(p.data_ptr(), scores.data_ptr(), rows, nk, int(heads), int(first_pos),
+                                           int(key_lo), int(window), float(scale), _DT3[dtype], _stream()),
+             "b200_masked_softmax")
+    return p
+
+
 def glu_clamped(x, alpha, limit):
     """x [rows, 2*inter] = (gate | up) -> g sigmoid(alpha g) (u + 1) with g = min(gate, limit), u = clamp(up, +-limit)."""
     _need_cuda(x)

@@ -22,6 +22,8 @@ linear layers of this step run on the library's single-CTA tcgen05 GEMM (ops.lin
 cuBLAS, whose 2-CTA clustered kernels cannot be placed next to a resident attention kernel.
 Fourth: ``state_slots`` -- int32 [num_seqs], the state slot of every sequence of the step (hybrid models:
 recurrent state and convolution tails live in per-slot rows; None for models without such state).
+Fifth: ``host_spans`` -- prefill steps: [(first token row, tokens, keys)] per sequence as python ints, for layers
+that launch per sequence (attention composed of library products).
 """
 from __future__ import annotations
 
@@ -47,6 +49,7 @@ class Context:
     decode_attn_ctas: int = 0
     own_gemm: bool = False
     state_slots: torch.Tensor | None = None
+    host_spans: list | None = None
 
 
 _current = Context()
@@ -59,11 +62,11 @@ def get_context() -> Context:
 def set_context(is_prefill, cu_seqlens_q=None, cu_seqlens_k=None, max_seqlen_q=0, max_seqlen_k=0,
                 slot_mapping=None, context_lens=None, block_tables=None, is_enforce_eager=None,
                 real_bs=None, block_size=None, paged_prefill=False, decode_attn_ctas=0, own_gemm=False,
-                state_slots=None) -> None:
+                state_slots=None, host_spans=None) -> None:
     global _current
     _current = Context(is_prefill, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k,
                        slot_mapping, context_lens, block_tables, is_enforce_eager, real_bs,
-                       block_size, paged_prefill, decode_attn_ctas, own_gemm, state_slots)
+                       block_size, paged_prefill, decode_attn_ctas, own_gemm, state_slots, host_spans)
 
 
 def reset_context() -> None:

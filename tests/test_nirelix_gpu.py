@@ -662,3 +662,49 @@ def test_latent_rows_norms_rotation_and_cache_write():
                           O.rotate(dkv[:, None, rank:].to(F64), pos, rot, base, True)[:, 0]], 1)
         assert torch.allclose(kc.cpu().to(F64), want, atol=1e-5)
         assert torch.allclose(cache.view(64, -1)[flat.long()].cpu().to(F64), want, atol=1e-5)
+
+
+def test_latent_prompts_on_library_products():
+    """Prompt portions of a 16-bit model run as library products around the masked softmax kernel: a 150-token
+    portion that continues 60 cached tokens (three query chunks of 64, key ranges that start inside the window), a
+    second whole sequence, and a short portion beside them, over a shuffled block table; same loud key at the
+    window's edge as in the kernel's own test."""
+    from nanovllm import ops
+    from nanovllm.layers.seq_mixers import LatentAttention
+    from nanovllm.utils.context import reset_context, set_context
+    dtype, window, rank, dim, H, bs = torch.bfloat16, 19, 24, 40, 3, 16
+    lens, starts = [210, 100, 30], [60, 0, 21]                # tokens in all, tokens already cached
+    stars = [97, 50, 3]
+    cases = [_latent_case(n, window, st, dtype, seed=5 + i) for i, (n, st) in enumerate(zip(lens, stars))]
+    attn = LatentAttention(H, dim - rank - 4, 4 + 0, 8, rank, 0.5, window=window)      # sizes only matter as rank + rot = 40
+    attn.rot = dim - rank
+    attn.PRODUCT_CHUNK = 64
+    nb = sum(-(-n // bs) for n in lens)
+    order = list(range(nb))
+    random.Random(3).shuffle(order)
+    attn.k_cache = torch.zeros(nb + 1, bs, dim, dtype=dtype, device="cuda")
+    tables, at = [], 0
+    for (q, rows, want), n in zip(cases, lens):
+        blocks = order[at:at + -(-n // bs)]
+        at += len(blocks)
+        tables.append(blocks + [-1] * (14 - len(blocks)))
+        for j in range(n):
+            attn.k_cache[blocks[j // bs], j % bs] = rows[j].to(dtype)
+    q_lens = [n - s for n, s in zip(lens, starts)]
+    cu_q = [0] + list(torch.tensor(q_lens).cumsum(0).tolist())
+    cu_k = [0] + list(torch.tensor(lens).cumsum(0).tolist())
+    dev_i32 = lambda x: torch.tensor(x, dtype=torch.int32).cuda()
+    set_context(True, cu_seqlens_q=dev_i32(cu_q), cu_seqlens_k=dev_i32(cu_k), max_seqlen_q=max(q_lens),
+                max_seqlen_k=max(lens), block_tables=dev_i32(tables), block_size=bs,
+                host_spans=[(cu_q[i], q_lens[i], lens[i]) for i in range(3)])
+    try:
+        from nanovllm.utils.context import get_context
+        qx = torch.cat([c[0][s:] for c, s in zip(cases, starts)]).to(dtype).cuda()
+        got = attn._prefill_by_products(qx, None, get_context(), True).cpu().to(F64).view(-1, H, rank)
+    finally:
+        reset_context()
+    want = torch.cat([c[2][s:] for c, s in zip(cases, starts)])
+    assert float((got - want).abs().max()) < 2e-2
+    edge = stars[0] + window - 1 - starts[0]                  # row of the last query that still sees the loud key
+    assert float((got[edge, 0] - cases[0][1][stars[0], :rank]).abs().max()) < 3e-2
+    assert float((got[edge + 1, 0] - cases[0][1][stars[0], :rank]).abs().max()) > 0.3
