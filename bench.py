@@ -789,6 +789,11 @@ def nirelix_kernel_table(width, head_dim, tokens, seqs, peak_gbs):
                                                                          spans, H, H, head_dim, head_dim, st, slots,
                                                                          decay=decay, act_silu=True),
             T * nq * (3 * 2 + 4) + state_bytes, flops=4.0 * T * H * head_dim * head_dim)
+        o32, gate = rnd(T, nq), rnd(T, nq).to(bf)
+        ones = torch.ones(nq, device=dev)
+        add("gated_norm(a norm per head, silu gate)", step,
+            lambda: ops.gated_norm(o32, gate, ones, 1e-6, groups=H, gate_act="silu"), T * nq * 8,
+            "gated_norm(one norm per row)", lambda: ops.gated_norm(o32, gate, ones, 1e-6), T * nq * 8)
         # delta rule: preparation, then the recurrence (like: the selective recurrence, which also decays per token)
         ngk = G * head_dim
         qkc = rnd(T, 2 * ngk + nq).to(bf)

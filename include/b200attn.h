@@ -530,12 +530,15 @@ int b200_latent_kv_prep(void* cq, void* kc, void* cache, const int32_t* slots, i
                         int32_t tokens, int32_t q_rank, int32_t rank, int32_t rot, int32_t dims, double base,
                         int32_t interleaved, float eps, int32_t dtype, b200_stream_t stream);
 
-/* Softmax over a block of fp32 scores s [rows, nk] of `heads` query heads per token against keys key_lo ..
- * key_lo + nk - 1 of one sequence: row r is the token at position first_pos + r / heads and sees key j iff
- * key_lo + j <= pos and (window == 0 or key_lo + j > pos - window). p [rows, nk] (dtype) = softmax(scale s) over the
- * visible keys, 0 elsewhere. scale > 0. */
+/* Softmax over a block of fp32 scores s [rows, nk] of `heads` query heads per token. ctx_lens == NULL: the rows
+ * are consecutive tokens of one sequence, row r at position first_pos + r / heads, column j the key at position
+ * key_lo + j. ctx_lens given (int32 per sequence): row r belongs to sequence r / heads, whose token is at position
+ * ctx_lens[.] - 1 (0: padded row, zeros), column j the key at position pos - nk + 1 + j. A key at position kp is
+ * visible iff 0 <= kp <= pos and (window == 0 or kp > pos - window). p [rows, nk] (dtype) = softmax(scale s) over
+ * the visible keys, 0 elsewhere. scale > 0. */
 int b200_masked_softmax(void* p, const float* s, int64_t rows, int32_t nk, int32_t heads, int32_t first_pos,
-                        int32_t key_lo, int32_t window, float scale, int32_t dtype, b200_stream_t stream);
+                        int32_t key_lo, int32_t window, float scale, const int32_t* ctx_lens, int32_t dtype,
+                        b200_stream_t stream);
 
 /* out[r, i] = g sigmoid(alpha g) (u + 1), g = min(x[r, i], limit), u = clamp(x[r, inter + i], -limit, limit). */
 int b200_glu_clamped(void* out, const void* x, int32_t rows, int32_t inter, float alpha, float limit,

@@ -491,6 +491,52 @@ gated_norm_vec_kernel(T* __restrict__ out, const Y* __restrict__ y, const T* __r
   }
 }
 
+// groups of at most 512 elements (one norm per head): one WARP per (row, group), 8 per CTA, no shared memory
+template <typename T, typename Y>
+__global__ void __launch_bounds__(256)
+gated_norm_warp_kernel(T* __restrict__ out, const Y* __restrict__ y, const T* __restrict__ gate,
+                       int64_t gate_stride, const float* __restrict__ w, float eps, int64_t rows, int n, int groups,
+                       int gate_first, int gate_act) {
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (unit >= rows * groups) return;
+  const int64_t r = unit / groups;
+  const int len = n / groups, lo = (int)(unit % groups) * len;
+  const Y* yr = y + r * n + lo;
+  const T* gr = gate + r * gate_stride + lo;
+  T* o = out + r * n + lo;
+  constexpr int kV = 2;
+  float val[kV][8], gv[kV][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int m = 0; m < kV; ++m) {
+    const int vi = lane + m * 32;
+    if (vi * 8 < len) {
+      load8<Y>(yr + vi * 8, val[m]);
+      load8<T>(gr + vi * 8, gv[m]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        gv[m][e] = gate_act == 1 ? silu_f(gv[m][e]) : sigmoid_f(gv[m][e]);
+        if (gate_first) val[m][e] *= gv[m][e];
+        ss += val[m][e] * val[m][e];
+      }
+    }
+  }
+  const float rstd = 1.0f / sqrtf(warp_sum(ss) / (float)len + eps);
+#pragma unroll
+  for (int m = 0; m < kV; ++m) {
+    const int vi = lane + m * 32;
+    if (vi * 8 < len) {
+      float ov[8], wv[8];
+      load8<float>(w + lo + vi * 8, wv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ov[e] = gate_first ? val[m][e] * rstd * wv[e] : val[m][e] * rstd * wv[e] * gv[m][e];
+      store8<T>(o + vi * 8, ov);
+    }
+  }
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -609,6 +655,19 @@ extern "C" int b200_gated_norm(void* out, const void* y, int32_t y_is_f32, const
   const int len = n / g;
   if (len % 8 == 0 && len <= 4096 && n % 8 == 0 && gate_stride % 8 == 0 && aligned16(out) && aligned16(y) &&
       aligned16(gate) && (!weight || aligned16(weight))) {
+    if (weight && g > 1 && len <= 512) {               // a norm per head: warps, not CTAs, per group
+      const int64_t units = (int64_t)rows * g;
+      const dim3 wgrid((unsigned)((units + 7) / 8));
+      B200_DISPATCH_3(dtype, T, {
+        if (y_is_f32)
+          launch_pdl(gated_norm_warp_kernel<T, float>, wgrid, dim3(256), 0, (cudaStream_t)stream, (T*)out,
+                     (const float*)y, (const T*)gate, gate_stride, weight, eps, (int64_t)rows, n, g, gate_first, gate_act);
+        else
+          launch_pdl(gated_norm_warp_kernel<T, T>, wgrid, dim3(256), 0, (cudaStream_t)stream, (T*)out, (const T*)y,
+                     (const T*)gate, gate_stride, weight, eps, (int64_t)rows, n, g, gate_first, gate_act);
+      });
+      return finish_launch();
+    }
     const int threads = len / 8 >= 256 ? 256 : ((len / 8 + 31) / 32) * 32;
     B200_DISPATCH_3(dtype, T, {
       if (y_is_f32)

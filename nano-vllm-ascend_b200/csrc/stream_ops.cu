@@ -98,6 +98,93 @@ stream_mix_norm_kernel(const StreamMixParams P) {
   }
 }
 
+// The same with the stream count as a template parameter and 4 elements per thread and step (hidden % 4 == 0): the
+// streams move as 16-byte vectors and the mixing loops are fully unrolled without predicates.
+template <typename T, int kS>
+__global__ void __launch_bounds__(256)
+stream_mix_norm_vec_kernel(const StreamMixParams P) {
+  extern __shared__ __align__(16) float su[];         // [hidden]
+  __shared__ float red[32];
+  __shared__ float smix[kS * kS], sout[kS], sin_[kS];
+  pdl_wait();
+  const int hidden = P.hidden, nv = hidden / 4;
+  if (threadIdx.x < kS * kS) smix[threadIdx.x] = P.mix != nullptr ? P.mix[threadIdx.x] : 0.f;
+  if (threadIdx.x < kS) {
+    sout[threadIdx.x] = P.out_w != nullptr ? P.out_w[threadIdx.x] : 0.f;
+    sin_[threadIdx.x] = P.in_w != nullptr ? P.in_w[threadIdx.x] : 1.f;
+  }
+  __syncthreads();
+  float4* xr = reinterpret_cast<float4*>(P.x + (int64_t)blockIdx.x * kS * hidden);
+  const T* yr = P.y != nullptr ? (const T*)P.y + (int64_t)blockIdx.x * hidden : nullptr;
+  float part = 0.f;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    float xs[kS][4];
+#pragma unroll
+    for (int s = 0; s < kS; ++s) {
+      const float4 v = xr[(int64_t)s * nv + i];
+      xs[s][0] = v.x, xs[s][1] = v.y, xs[s][2] = v.z, xs[s][3] = v.w;
+    }
+    float u[4] = {0.f, 0.f, 0.f, 0.f};
+    if (yr != nullptr) {
+      float y[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) y[e] = to_f32<T>(yr[i * 4 + e]);
+#pragma unroll
+      for (int t = 0; t < kS; ++t) {
+        float acc[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          acc[e] = 0.f;
+#pragma unroll
+          for (int s = 0; s < kS; ++s) acc[e] += smix[s * kS + t] * xs[s][e];
+          acc[e] += sout[t] * y[e];
+          u[e] += sin_[t] * acc[e];
+        }
+        xr[(int64_t)t * nv + i] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      }
+    } else {
+#pragma unroll
+      for (int t = 0; t < kS; ++t)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) u[e] += sin_[t] * xs[t][e];
+    }
+    reinterpret_cast<float4*>(su)[i] = make_float4(u[0], u[1], u[2], u[3]);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) part += P.kind == 0 ? u[e] : u[e] * u[e];
+  }
+  if (P.sum_out != nullptr)
+    for (int i = threadIdx.x; i < nv; i += blockDim.x)
+      reinterpret_cast<float4*>(P.sum_out + (int64_t)blockIdx.x * hidden)[i] = reinterpret_cast<float4*>(su)[i];
+  if (P.w == nullptr) return;
+  T* h = (T*)P.h + (int64_t)blockIdx.x * hidden;
+  float mean = 0.f, rstd;
+  if (P.kind == 0) {
+    mean = cta_sum(part, red) / (float)hidden;
+    float sq = 0.f;
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+      const float4 v = reinterpret_cast<float4*>(su)[i];
+      sq += (v.x - mean) * (v.x - mean) + (v.y - mean) * (v.y - mean) + (v.z - mean) * (v.z - mean) +
+            (v.w - mean) * (v.w - mean);
+    }
+    rstd = 1.0f / sqrtf(cta_sum(sq, red) / (float)hidden + P.eps);
+  } else {
+    rstd = 1.0f / sqrtf(cta_sum(part, red) / (float)hidden + P.eps);
+  }
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    const float4 v = reinterpret_cast<float4*>(su)[i];
+    const float4 w = reinterpret_cast<const float4*>(P.w)[i];
+    const float uu[4] = {v.x, v.y, v.z, v.w}, ww[4] = {w.x, w.y, w.z, w.w};
+    float bb[4] = {0.f, 0.f, 0.f, 0.f};
+    if (P.kind == 0 && P.b != nullptr) {
+      const float4 b = reinterpret_cast<const float4*>(P.b)[i];
+      bb[0] = b.x, bb[1] = b.y, bb[2] = b.z, bb[3] = b.w;
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      h[i * 4 + e] = from_f32<T>(P.kind == 0 ? (uu[e] - mean) * rstd * ww[e] + bb[e] : uu[e] * rstd * (P.offset + ww[e]));
+  }
+}
+
 // ------------------------------------------------------------------ rotary positions
 struct RotaryParams {
   const void* in;          // element type; head hd of token t starts at in + t * in_stride + hd * in_head
@@ -287,21 +374,30 @@ glu_clamped_vec_kernel(T* __restrict__ out, const T* __restrict__ x, int64_t row
 }
 
 // ------------------------------------------------------------------ masked softmax over a block of scores
-// One warp per row of s [rows, nk] (fp32 scores of `heads` query heads per token against keys key_lo .. key_lo + nk - 1
-// of one sequence): row r belongs to the token at position first_pos + r / heads and sees key j iff
-// key_lo + j <= pos and (window == 0 or key_lo + j > pos - window). p = softmax(scale * s) over the visible keys,
-// written in the element type; hidden keys get 0.
+// One warp per row of s [rows, nk] (fp32 scores of `heads` query heads per token against nk keys). Two forms:
+//   ctx_lens == nullptr: the rows are consecutive tokens of ONE sequence, row r at position first_pos + r / heads,
+//                        column j is the key at position key_lo + j;
+//   ctx_lens != nullptr: row r belongs to sequence r / heads, whose one token sits at position ctx_lens[.] - 1 (0 keys:
+//                        a padded row, all zeros), and column j is the key at position pos - nk + 1 + j (the last nk
+//                        positions, gathered by the caller; negative positions do not exist).
+// A key at position kp is visible iff 0 <= kp <= pos and (window == 0 or kp > pos - window). p = softmax(scale * s)
+// over the visible keys, written in the element type; hidden keys get 0.
 template <typename T>
 __global__ void __launch_bounds__(128)
 masked_softmax_kernel(T* __restrict__ p, const float* __restrict__ s, int64_t rows, int nk, int heads, int first_pos,
-                      int key_lo, int window, float scale) {
+                      int key_lo, int window, float scale, const int* __restrict__ ctx_lens) {
   pdl_wait();
   const int lane = threadIdx.x & 31;
   const int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (r >= rows) return;
-  const int pos = first_pos + (int)(r / heads);
-  const int hi = min(nk, pos - key_lo + 1);                                  // visible: [lo, hi)
-  const int lo = window > 0 ? max(0, pos - window + 1 - key_lo) : 0;
+  int pos = first_pos + (int)(r / heads);
+  if (ctx_lens != nullptr) {
+    pos = ctx_lens[r / heads] - 1;
+    key_lo = pos - nk + 1;
+  }
+  const int hi = pos < 0 ? 0 : min(nk, pos - key_lo + 1);                    // visible: [lo, hi)
+  int lo = max(0, -key_lo);
+  if (window > 0) lo = max(lo, pos - window + 1 - key_lo);
   const float* sr = s + r * nk;
   T* pr = p + r * nk;
   float m = -INFINITY;
@@ -320,15 +416,15 @@ masked_softmax_kernel(T* __restrict__ p, const float* __restrict__ s, int64_t ro
 using namespace b200;
 
 extern "C" int b200_masked_softmax(void* p, const float* s, int64_t rows, int32_t nk, int32_t heads,
-                                   int32_t first_pos, int32_t key_lo, int32_t window, float scale, int32_t dtype,
-                                   b200_stream_t stream) {
-  B200_RETURN_IF(rows < 0 || nk <= 0 || heads <= 0 || first_pos < 0 || key_lo < 0 || window < 0 || scale <= 0.f,
+                                   int32_t first_pos, int32_t key_lo, int32_t window, float scale,
+                                   const int32_t* ctx_lens, int32_t dtype, b200_stream_t stream) {
+  B200_RETURN_IF(rows < 0 || nk <= 0 || heads <= 0 || first_pos < 0 || window < 0 || scale <= 0.f,
                  B200_ERR_BAD_SHAPE);
   if (rows == 0) return B200_OK;
   B200_RETURN_IF(!p || !s, B200_ERR_NULL_POINTER);
   B200_DISPATCH_3(dtype, T, launch_pdl(masked_softmax_kernel<T>, dim3((unsigned)((rows + 3) / 4)), dim3(128), 0,
                                        (cudaStream_t)stream, (T*)p, s, rows, nk, heads, first_pos, key_lo, window,
-                                       scale));
+                                       scale, ctx_lens));
   return finish_launch();
 }
 
@@ -344,6 +440,26 @@ extern "C" int b200_stream_mix_norm(void* h, float* x, const void* y, const floa
   P.x = x, P.y = y, P.mix = mix, P.out_w = out_w, P.in_w = in_w, P.w = w, P.b = b, P.h = h, P.sum_out = sum_out;
   P.eps = eps, P.offset = offset, P.S = streams, P.hidden = hidden, P.kind = kind;
   const size_t smem = (size_t)hidden * sizeof(float);
+  const bool vec = hidden % 4 == 0 && smem <= 40 * 1024 && aligned16(x) && (!w || aligned16(w)) &&
+                   (!b || aligned16(b)) && (!sum_out || aligned16(sum_out));
+#define B200_STREAMS_VEC(N)                                                                                        \
+  case N:                                                                                                          \
+    B200_DISPATCH_3(dtype, T, launch_pdl(stream_mix_norm_vec_kernel<T, N>, dim3(rows), dim3(256), smem,            \
+                                         (cudaStream_t)stream, P));                                                \
+    return finish_launch();
+  if (vec) {
+    switch (streams) {
+      B200_STREAMS_VEC(1)
+      B200_STREAMS_VEC(2)
+      B200_STREAMS_VEC(3)
+      B200_STREAMS_VEC(4)
+      B200_STREAMS_VEC(5)
+      B200_STREAMS_VEC(6)
+      B200_STREAMS_VEC(7)
+      B200_STREAMS_VEC(8)
+    }
+  }
+#undef B200_STREAMS_VEC
   B200_DISPATCH_3(dtype, T, {
     if (smem > 40 * 1024)
       cudaFuncSetAttribute(stream_mix_norm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -237,6 +237,8 @@ class LatentAttention(nn.Module):
         if (ctx.is_prefill and ctx.host_spans is not None and qx.dtype != torch.float32 and not self.force_generic
                 and ctx.max_seqlen_q >= self.PRODUCT_MIN_TOKENS):
             lat = self._prefill_by_products(qx, kc, ctx, paged)
+        elif (not ctx.is_prefill and paged and 0 < self.window <= self.DECODE_WINDOW_MAX and not self.force_generic):
+            lat = self._decode_window_by_products(qx, ctx)
         elif paged:
             lat = ops.attn_generic(qx, self.k_cache, None, spans, self.scale, 1, R, block_tables=ctx.block_tables,
                                    window=self.window)
@@ -244,6 +246,27 @@ class LatentAttention(nn.Module):
             lat = ops.attn_generic(qx, kc.unsqueeze(1), None, spans, self.scale, 1, R, window=self.window)
         out = torch.bmm(lat.view(T, H, R).transpose(0, 1), self.w_uv.transpose(1, 2))      # [H, T, vdim]
         return out.transpose(0, 1).reshape(T, H * self.vdim)
+
+    DECODE_WINDOW_MAX = 4096      # decode steps gather a window of at most this many rows per sequence
+
+    def _decode_window_by_products(self, qx, ctx):
+        """Decode steps inside a sliding window: every sequence sees at most `window` keys, so the step gathers the
+        last `window` cached rows of every sequence into one dense block (fixed shapes: capturable in a CUDA graph),
+        scores all heads against it with one batched library product (fp32 out), runs the masked softmax kernel
+        (rows before a sequence's start and padded graph rows are hidden) and multiplies by the latent part of the same
+        rows. Without a window the generic kernel reads the cache through the block table instead."""
+        B, H, D = qx.shape
+        W, R, bs = self.window, self.rank, ctx.block_size
+        pos = ctx.context_lens.long() - 1                                    # -1 on padded rows
+        j = (pos[:, None] - (W - 1) + torch.arange(W, device=qx.device)).clamp(min=0)
+        blocks = ctx.block_tables.gather(1, j // bs).clamp(min=0).long()
+        rows = self.k_cache.view(-1, D)[(blocks * bs + j % bs).view(-1)].view(B, W, D)
+        if qx.dtype == torch.float32:
+            scores = torch.bmm(qx, rows.transpose(1, 2))
+        else:
+            scores = torch.bmm(qx, rows.transpose(1, 2), out_dtype=torch.float32)
+        p = ops.masked_softmax(scores.view(B * H, W), H, 0, 0, self.scale, W, qx.dtype, ctx_lens=ctx.context_lens)
+        return torch.bmm(p.view(B, H, W), rows[:, :, :R]).reshape(B, H * R)
 
     PRODUCT_MIN_TOKENS = 64       # longest portion of the step from which prompts run on library products
     PRODUCT_CHUNK = 512           # query tokens per product
@@ -274,14 +297,15 @@ class LatentAttention(nn.Module):
                 c1 = min(ql, c0 + self.PRODUCT_CHUNK)
                 lo = max(0, first + c0 - self.window + 1) if self.window else 0
                 hi = first + c1
+                lo = hi - -(-(hi - lo) // 8) * 8           # a multiple of 8 keys (16-byte rows for the products); a
+                j = torch.arange(lo, hi, device=qx.device).clamp(min=0)     # range that starts before 0 is hidden
                 if paged:
-                    j = torch.arange(lo, hi, device=qx.device)
                     rows = flat[ctx.block_tables[s][j // bs].long() * bs + j % bs]
                 else:                                  # no cache bound: the span's keys are this step's rows
-                    rows = kc[q0 + lo:q0 + hi]
+                    rows = kc[q0 + j]
                 scores = torch.mm(qx[q0 + c0:q0 + c1].reshape(-1, D), rows.t(), out_dtype=torch.float32)
                 p = ops.masked_softmax(scores, H, first + c0, lo, self.scale, self.window, qx.dtype)
-                lat[q0 + c0:q0 + c1] = torch.mm(p, rows[:, :R]).view(-1, H * R)
+                lat[q0 + c0:q0 + c1] = torch.mm(p, rows[:, :R].contiguous()).view(-1, H * R)
         return lat
 
 

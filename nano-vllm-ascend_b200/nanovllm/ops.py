@@ -904,18 +904,22 @@ def latent_kv_prep(dq, dkv, wq, wc, positions, rank, rot, dims, base, interleave
     return cq, kc
 
 
-def masked_softmax(scores, heads, first_pos, key_lo, scale, window, dtype):
-    """scores fp32 [rows, nk]: `heads` query heads per token (row r = token first_pos + r // heads) against keys
-    key_lo .. key_lo + nk - 1 of one sequence -> softmax(scale * scores) over the causally visible keys inside the
-    window (0: none), in `dtype`; hidden keys get 0."""
-    _need_cuda(scores)
+def masked_softmax(scores, heads, first_pos, key_lo, scale, window, dtype, ctx_lens=None):
+    """scores fp32 [rows, nk] of `heads` query heads per token -> softmax(scale * scores) over the visible keys in
+    `dtype`, hidden keys 0. Without ctx_lens the rows are consecutive tokens of one sequence (row r at position
+    first_pos + r // heads, column j the key at position key_lo + j); with ctx_lens (int32 per sequence) row r is the
+    one token of sequence r // heads at position ctx_lens - 1 and column j the key at position pos - nk + 1 + j. A key
+    is visible iff it exists, is not ahead of the token and lies inside the window (0: no window)."""
+    _need_cuda(scores, ctx_lens)
     if scores.dtype != torch.float32 or not scores.is_contiguous() or scores.dim() != 2:
         raise TypeError("scores are a contiguous fp32 matrix")
+    if ctx_lens is not None and (ctx_lens.dtype != torch.int32 or not ctx_lens.is_contiguous()):
+        raise TypeError("ctx_lens must be contiguous int32")
     rows, nk = scores.shape
     p = torch.empty(rows, nk, dtype=dtype, device=scores.device)
     _C.check(_C.load().b200_masked_softmax(p.data_ptr(), scores.data_ptr(), rows, nk, int(heads), int(first_pos),
-                                           int(key_lo), int(window), float(scale), _DT3[dtype], _stream()),
-             "b200_masked_softmax")
+                                           int(key_lo), int(window), float(scale), _ptr(ctx_lens), _DT3[dtype],
+                                           _stream()), "b200_masked_softmax")
     return p
 
 

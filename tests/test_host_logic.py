@@ -37,7 +37,7 @@ def test_ctypes_prototypes_match_the_header_signatures():
     decls = re.findall(r"\b(?:int|int64_t|size_t|void|const char\*)\s+\**(b200_\w+)\s*\(([^;]*?)\)\s*;",
                        header, flags=re.S)
     assert len(decls) >= 30
-    scalar = {"float": ctypes.c_float, "int32_t": ctypes.c_int32, "int": ctypes.c_int32,
+    scalar = {"float": ctypes.c_float, "double": ctypes.c_double, "int32_t": ctypes.c_int32, "int": ctypes.c_int32,
               "int64_t": ctypes.c_int64, "uint64_t": ctypes.c_uint64, "size_t": ctypes.c_size_t}
 
     def ctype_of(arg: str):

@@ -123,10 +123,17 @@ def row_err(got, want):
     return d.pow(2).mean(-1).sqrt() / w.pow(2).mean(-1).sqrt()
 
 
-def close(got, want, dtype, strict=True):
+def fp32_noise(cfg, tensors, toks, want):
+    """Per row, the error of the oracle itself when it runs in fp32: some prompts drive a norm's input near zero and
+    amplify any fp32 rounding; there an fp32 engine is asked to stay within 3 times of that, not below 2e-4."""
+    return row_err(O.forward(cfg, {k: v.float() for k, v in tensors.items()}, toks), want)
+
+
+def close(got, want, dtype, strict=True, noise=None):
     e = row_err(got, want)
     if dtype == "float32":
-        return float(e.max()) < 2e-4
+        limit = torch.full_like(e, 2e-4) if noise is None else torch.maximum(torch.full_like(e, 2e-4), 3 * noise)
+        return bool((e < limit).all())
     if strict:
         return float(e.pow(2).mean().sqrt()) < 3e-2 and float(e.max()) < 0.2
     # a model that chooses experts: bf16 rounding may flip a close choice for a token, so a few rows may differ
@@ -213,6 +220,7 @@ def test_unequal_batches_and_reused_slots(tmp_path_factory, name, dtype):
     lens = [37, 90, 5, 64, 51, 33, 18]
     reqs = {f"r{i}": tokens_of(cfg, n, 10 + i) for i, n in enumerate(lens)}
     want = {k: O.forward(cfg, tensors, v) for k, v in reqs.items()}
+    noise = {k: fp32_noise(cfg, tensors, v, want[k]) if dtype == "float32" else None for k, v in reqs.items()}
     at = {k: 0 for k in reqs}
     got = {k: [] for k in reqs}
     waiting, live = list(reqs), []
@@ -246,7 +254,8 @@ def test_unequal_batches_and_reused_slots(tmp_path_factory, name, dtype):
     assert sum(len(t) for t in tables.values()) > pool                           # and so were blocks
     assert len(bm.free_block_ids) == pool and len(bm.free_state_slots) == 4      # everything was given back
     for k in reqs:
-        assert close(torch.cat(got[k]), want[k], dtype, STRICT_BF16[name]), (k, float(row_err(torch.cat(got[k]), want[k]).max()))
+        assert close(torch.cat(got[k]), want[k], dtype, STRICT_BF16[name], noise[k]), \
+            (k, float(row_err(torch.cat(got[k]), want[k]).max()))
 
 
 def test_long_decoding(tmp_path_factory):
@@ -708,3 +717,45 @@ def test_latent_prompts_on_library_products():
     edge = stars[0] + window - 1 - starts[0]                  # row of the last query that still sees the loud key
     assert float((got[edge, 0] - cases[0][1][stars[0], :rank]).abs().max()) < 3e-2
     assert float((got[edge + 1, 0] - cases[0][1][stars[0], :rank]).abs().max()) > 0.3
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_latent_decode_rows_inside_a_window(dtype):
+    """Decode steps gather each sequence's last `window` rows: sequences shorter than the window, exactly at it, with
+    the loud key just inside and just outside, and a padded row (0 keys) in one launch."""
+    from nanovllm.layers.seq_mixers import LatentAttention
+    from nanovllm.utils.context import get_context, reset_context, set_context
+    window, rank, dim, H, bs, star = 19, 24, 40, 3, 16, 37
+    q, rows, want = _latent_case(80, window, star, dtype)
+    attn = LatentAttention(H, 12, 16, 8, rank, 0.5, window=window)
+    table = [7, 2, 5, 0, 3]
+    attn.k_cache = torch.zeros(9, bs, dim, dtype=dtype, device="cuda")
+    for j in range(80):
+        attn.k_cache[table[j // bs], j % bs] = rows[j].to(dtype)
+    at = [4, window - 1, window, star + window - 1, star + window, 79]              # positions of the decoded tokens
+    ctx_lens = [p + 1 for p in at] + [0]
+    qx = torch.cat([q[at], torch.zeros(1, H, dim, dtype=F64)]).to(dtype).cuda()
+    tables = torch.tensor([table] * 6 + [[-1] * 5], dtype=torch.int32).cuda()
+    set_context(False, context_lens=torch.tensor(ctx_lens, dtype=torch.int32).cuda(), block_tables=tables, block_size=bs)
+    try:
+        got = attn._decode_window_by_products(qx, get_context()).cpu().to(F64).view(-1, H, rank)
+    finally:
+        reset_context()
+    assert float((got[:6] - want[at]).abs().max()) < (1e-5 if dtype == torch.float32 else 2e-2)
+    assert float(got[6].abs().max()) == 0.0
+    assert float((got[3, 0] - rows[star, :rank]).abs().max()) < 3e-2 < float((got[4, 0] - rows[star, :rank]).abs().max())
+
+
+@pytest.mark.parametrize("act", ["sigmoid", "silu"])
+def test_norm_per_head_and_gate(act):
+    """One RMS norm per head (a warp per head), a weight shared by the heads, then the gate."""
+    from nanovllm import ops
+    g = torch.Generator().manual_seed(11)
+    rows, H, dv, eps = 9, 4, 24, 1e-4
+    y, gate = torch.randn(rows, H * dv, generator=g) * 3, torch.randn(rows, H * dv + 8, generator=g)
+    w = 1 + 0.2 * torch.randn(dv, generator=g)
+    gv = gate[:, 8:].to(F64)
+    want = (O.rms_unit(y.to(F64).view(rows, H, dv), eps) * w.to(F64)).reshape(rows, -1) * \
+        (torch.sigmoid(gv) if act == "sigmoid" else O.silu(gv))
+    got = ops.gated_norm(_dev(y), _dev(gate)[:, 8:], _dev(w.repeat(H)), eps, groups=H, gate_first=False, gate_act=act)
+    assert torch.allclose(got.cpu().to(F64), want, atol=1e-5)
