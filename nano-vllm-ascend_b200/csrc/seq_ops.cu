@@ -491,18 +491,21 @@ gated_norm_vec_kernel(T* __restrict__ out, const Y* __restrict__ y, const T* __r
   }
 }
 
-// groups of at most 512 elements (one norm per head): one WARP per (row, group), 8 per CTA, no shared memory
+// groups of at most 512 elements (one norm per head): GL = 1 .. 32 adjacent lanes per (row, group) -- the smallest power
+// of two that covers the group with 8 elements per lane (two steps per lane above 256 elements) -- so that every lane of
+// a warp works; sums by xor shuffles inside the lane group, no shared memory
 template <typename T, typename Y>
 __global__ void __launch_bounds__(256)
 gated_norm_warp_kernel(T* __restrict__ out, const Y* __restrict__ y, const T* __restrict__ gate,
                        int64_t gate_stride, const float* __restrict__ w, float eps, int64_t rows, int n, int groups,
-                       int gate_first, int gate_act) {
+                       int gate_first, int gate_act, int gl) {
   pdl_wait();
-  const int lane = threadIdx.x & 31;
-  const int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (unit >= rows * groups) return;
-  const int64_t r = unit / groups;
-  const int len = n / groups, lo = (int)(unit % groups) * len;
+  const int lane = threadIdx.x & 31, sub = lane % gl;
+  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t unit = warp * (32 / gl) + lane / gl;
+  const bool live = unit < rows * groups;
+  const int64_t r = live ? unit / groups : 0;
+  const int len = n / groups, lo = live ? (int)(unit % groups) * len : 0;
   const Y* yr = y + r * n + lo;
   const T* gr = gate + r * gate_stride + lo;
   T* o = out + r * n + lo;
@@ -511,8 +514,8 @@ gated_norm_warp_kernel(T* __restrict__ out, const Y* __restrict__ y, const T* __
   float ss = 0.f;
 #pragma unroll
   for (int m = 0; m < kV; ++m) {
-    const int vi = lane + m * 32;
-    if (vi * 8 < len) {
+    const int vi = sub + m * gl;
+    if (live && vi * 8 < len && (m == 0 || gl == 32)) {
       load8<Y>(yr + vi * 8, val[m]);
       load8<T>(gr + vi * 8, gv[m]);
 #pragma unroll
@@ -523,11 +526,12 @@ gated_norm_warp_kernel(T* __restrict__ out, const Y* __restrict__ y, const T* __
       }
     }
   }
-  const float rstd = 1.0f / sqrtf(warp_sum(ss) / (float)len + eps);
+  for (int off = gl >> 1; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  const float rstd = 1.0f / sqrtf(ss / (float)len + eps);
 #pragma unroll
   for (int m = 0; m < kV; ++m) {
-    const int vi = lane + m * 32;
-    if (vi * 8 < len) {
+    const int vi = sub + m * gl;
+    if (live && vi * 8 < len && (m == 0 || gl == 32)) {
       float ov[8], wv[8];
       load8<float>(w + lo + vi * 8, wv);
 #pragma unroll
@@ -656,15 +660,17 @@ extern "C" int b200_gated_norm(void* out, const void* y, int32_t y_is_f32, const
   if (len % 8 == 0 && len <= 4096 && n % 8 == 0 && gate_stride % 8 == 0 && aligned16(out) && aligned16(y) &&
       aligned16(gate) && (!weight || aligned16(weight))) {
     if (weight && g > 1 && len <= 512) {               // a norm per head: warps, not CTAs, per group
-      const int64_t units = (int64_t)rows * g;
-      const dim3 wgrid((unsigned)((units + 7) / 8));
+      int gl = 1;
+      while (gl * 8 < len && gl < 32) gl <<= 1;
+      const int64_t warps = ((int64_t)rows * g + 32 / gl - 1) / (32 / gl);
+      const dim3 wgrid((unsigned)((warps + 7) / 8));
       B200_DISPATCH_3(dtype, T, {
         if (y_is_f32)
           launch_pdl(gated_norm_warp_kernel<T, float>, wgrid, dim3(256), 0, (cudaStream_t)stream, (T*)out,
-                     (const float*)y, (const T*)gate, gate_stride, weight, eps, (int64_t)rows, n, g, gate_first, gate_act);
+                     (const float*)y, (const T*)gate, gate_stride, weight, eps, (int64_t)rows, n, g, gate_first, gate_act, gl);
         else
           launch_pdl(gated_norm_warp_kernel<T, T>, wgrid, dim3(256), 0, (cudaStream_t)stream, (T*)out, (const T*)y,
-                     (const T*)gate, gate_stride, weight, eps, (int64_t)rows, n, g, gate_first, gate_act);
+                     (const T*)gate, gate_stride, weight, eps, (int64_t)rows, n, g, gate_first, gate_act, gl);
       });
       return finish_launch();
     }

@@ -121,7 +121,8 @@ class LatentAttentionMixer(nn.Module):
         self.q_norm, self.kv_norm = small_param(self.q_rank, fill=1.0), small_param(self.rank, fill=1.0)
         self.q_up = ReplicatedLinear(self.q_rank, H * (d + dr))
         self.rot = Rotary(m["rot"]["dims"], m["rot"]["base"], interleaved=True)
-        self.attn = LatentAttention(H, d, dr, dv, self.rank, m["scale"], window=(m.get("mask") or {}).get("size", 0))
+        self.attn = LatentAttention(H, d, dr, dv, self.rank, m.get("scale", (d + dr) ** -0.5),
+                                    window=(m.get("mask") or {}).get("size", 0))
         self.gate = GatedNorm(H * dv, eps, norm=False)
         self.o_proj = RowParallelLinear(H * dv, width)
 

@@ -392,7 +392,7 @@ def test_grouped_sigmoid_router(E, top, count, keep):
     assert torch.allclose(w.gather(1, order_w), wg.gather(1, order_g), atol=1e-6)
 
 
-def _moe_case(W, ff, E, top, count, keep, dtype, fast, seed):
+def _moe_case(W, ff, E, top, count, keep, dtype, fast, seed, tokens=150):
     from nanovllm.layers.moe import GroupedSigmoidMoe
     cfg = {"architecture": "Nirelix", "vocab": 8, "width": W, "norm": {"eps": 1e-6},
            "layers": [dict(delta(1, 1, 8, 8, 2), mlp=moe(E, top, ff, count, keep, 1.3))]}
@@ -412,7 +412,7 @@ def _moe_case(W, ff, E, top, count, keep, dtype, fast, seed):
         m.w13.data[e, :ff].copy_(P[f"e{e}.gate"])
         m.w13.data[e, ff:].copy_(P[f"e{e}.up"])
         m.w2.data[e].copy_(P[f"e{e}.down"])
-    x = torch.randn(150, W, generator=torch.Generator().manual_seed(seed)).to(dtype)
+    x = torch.randn(tokens, W, generator=torch.Generator().manual_seed(seed)).to(dtype)
     want = O.moe_ff(x.to(F64), P, cfg["layers"][0]["mlp"])
     with torch.no_grad():
         got = m(x.cuda())
@@ -426,11 +426,12 @@ def test_mixture_of_experts_any_size_fp32():
     assert float(e.max()) < 1e-5
 
 
-@pytest.mark.parametrize("fast", [True, False])
-def test_mixture_of_experts_bf16_both_paths(fast):
-    """Width 128 and expert size 64 fit the tensor-core expert kernels (fast) and run on the generic ones as well;
-    a few tokens may choose differently than the float64 oracle after the input's rounding."""
-    e = _moe_case(128, 64, 8, 2, 2, 1, torch.bfloat16, fast, 3)
+@pytest.mark.parametrize("fast,tokens", [(True, 150), (True, 1000), (False, 150)])
+def test_mixture_of_experts_bf16_both_paths(fast, tokens):
+    """Width 128 and expert size 64 fit the tensor-core expert kernels (fast: the weight-streaming form for few rows
+    per expert, the grouped tcgen05 form for many) and run on the generic ones as well; a few tokens may choose
+    differently than the float64 oracle after the input's rounding."""
+    e = _moe_case(128, 64, 8, 2, 2, 1, torch.bfloat16, fast, 3, tokens)
     assert float(e.median()) < 1e-2 and float((e < 3e-2).double().mean()) > 0.9
 
 
