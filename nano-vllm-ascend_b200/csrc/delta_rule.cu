@@ -11,7 +11,8 @@
 // KPT <= 64 key rows of S in registers (NS = 1, 2 or 4 adjacent lanes share a column when kdim > 64). Per token it
 // makes two passes over its rows -- decay + the projection S^T k, then the rank-one write + the read-out S^T q --
 // with k, q, g read as float4 broadcasts from shared memory; the two dot products are finished with NS - 1
-// shuffles. Tokens are staged kDeltaTok at a time.
+// shuffles. Tokens are staged kDeltaTok at a time; where the rows allow 16-byte copies (VEC) the next batch arrives by
+// cp.async in a second set of buffers while the current one is consumed, otherwise batches are loaded in place.
 #include "seq_common.cuh"
 
 namespace b200 {
@@ -30,7 +31,12 @@ struct DeltaParams {
   int H, groups, kdim, vdim;
 };
 
-template <typename TV, int KPT, int NS>
+__device__ __forceinline__ void cp_async_4(uint32_t smem_addr, const void* gptr, bool pred) {
+  const int bytes = pred ? 4 : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_addr), "l"(gptr), "r"(bytes) : "memory");
+}
+
+template <typename TV, int KPT, int NS, bool VEC>
 __global__ void __launch_bounds__(128)
 delta_rule_kernel(const DeltaParams P) {
   extern __shared__ __align__(16) float smem[];
@@ -46,11 +52,14 @@ delta_rule_kernel(const DeltaParams P) {
   const bool col_ok = col < vdim;
   const bool warp_live = c0 + (int)((threadIdx.x & ~31u) / NS) < vdim;
   const int grp = h / (P.H / P.groups);
-  float* sq = smem;                                  // [kDeltaTok][KP]
-  float* sk = sq + kDeltaTok * KP;
-  float* sg = sk + kDeltaTok * KP;
-  float* sx = sg + kDeltaTok * KP;                   // [kDeltaTok][CC]
-  float* sb = sx + kDeltaTok * CC;                   // [kDeltaTok]
+  constexpr int NB = VEC ? 2 : 1;                    // sets of staging buffers
+  constexpr int QK = kDeltaTok * KP;
+  float* sq = smem;                                  // [NB][kDeltaTok][KP]
+  float* sk = sq + NB * QK;
+  float* sg = sk + NB * QK;
+  float* sb = sg + NB * QK;                          // [NB][kDeltaTok]
+  float* sx = sb + NB * kDeltaTok;                   // [kDeltaTok][CC] fp32 (in-place form)
+  TV* sxr = reinterpret_cast<TV*>(sb + NB * kDeltaTok);   // [2][kDeltaTok][CC] as stored (cp.async form)
 
   float S[KPT];
   float* slot = P.state != nullptr
@@ -69,29 +78,61 @@ delta_rule_kernel(const DeltaParams P) {
   const int vcols = min(CC, vdim - c0);
   const int64_t g_stride = (int64_t)P.H * kdim;
 
-  for (int t0 = 0; t0 < sp.q_len; t0 += kDeltaTok) {
+  auto issue = [&](int t0, int b) {                  // cp.async form: batch t0 into buffer set b (zero-filled padding)
     const int nt = min(kDeltaTok, sp.q_len - t0);
     const int64_t tok0 = sp.q_start + t0;
-    __syncthreads();                                 // the previous batch has been consumed
-    for (int e = threadIdx.x; e < kDeltaTok * KP; e += 128) {
-      const int tt = e / KP, i = e % KP;
+    constexpr int K4 = KP / 4, VE = 16 / (int)sizeof(TV);
+    for (int e = threadIdx.x; e < kDeltaTok * K4; e += 128) {
+      const int tt = e / K4, i = (e % K4) * 4;
       const bool ok = tt < nt && i < kdim;
-      sq[e] = ok ? q[(tok0 + tt) * P.q_stride + i] : 0.f;
-      sk[e] = ok ? k[(tok0 + tt) * P.k_stride + i] : 0.f;
-      sg[e] = ok ? g[(tok0 + tt) * g_stride + i] : 0.f;
+      const int64_t tok = tok0 + (tt < nt ? tt : 0);
+      const int ii = ok ? i : 0;
+      cp_async_16(smem_u32(sq + b * QK + tt * KP + i), q + tok * P.q_stride + ii, ok);
+      cp_async_16(smem_u32(sk + b * QK + tt * KP + i), k + tok * P.k_stride + ii, ok);
+      cp_async_16(smem_u32(sg + b * QK + tt * KP + i), g + tok * g_stride + ii, ok);
     }
-    for (int e = threadIdx.x; e < kDeltaTok * CC; e += 128) {
-      const int tt = e / CC, c = e % CC;
-      sx[e] = (tt < nt && c < vcols) ? to_f32<TV>(v[(tok0 + tt) * P.v_stride + c]) : 0.f;
+    for (int e = threadIdx.x; e < kDeltaTok * CC / VE; e += 128) {
+      const int tt = e / (CC / VE), c = (e % (CC / VE)) * VE;
+      const bool ok = tt < nt && c < vcols;
+      cp_async_16(smem_u32(sxr + (b * kDeltaTok + tt) * CC + c), v + (tok0 + (tt < nt ? tt : 0)) * P.v_stride + (ok ? c : 0), ok);
     }
-    if (threadIdx.x < kDeltaTok) sb[threadIdx.x] = threadIdx.x < nt ? P.beta[(tok0 + threadIdx.x) * P.H + h] : 0.f;
-    __syncthreads();
+    if (threadIdx.x < kDeltaTok) {
+      const bool ok = (int)threadIdx.x < nt;
+      cp_async_4(smem_u32(sb + b * kDeltaTok + threadIdx.x), P.beta + (tok0 + (ok ? threadIdx.x : 0)) * P.H + h, ok);
+    }
+    cp_async_commit();
+  };
+  if (VEC) issue(0, 0);
+  int b = 0;
+  for (int t0 = 0; t0 < sp.q_len; t0 += kDeltaTok, b ^= (VEC ? 1 : 0)) {
+    const int nt = min(kDeltaTok, sp.q_len - t0);
+    const int64_t tok0 = sp.q_start + t0;
+    if (VEC) {
+      cp_async_wait<0>();
+      __syncthreads();                               // batch b has landed everywhere; set b ^ 1 has been consumed
+      if (t0 + kDeltaTok < sp.q_len) issue(t0 + kDeltaTok, b ^ 1);
+    } else {
+      __syncthreads();                               // the previous batch has been consumed
+      for (int e = threadIdx.x; e < kDeltaTok * KP; e += 128) {
+        const int tt = e / KP, i = e % KP;
+        const bool ok = tt < nt && i < kdim;
+        sq[e] = ok ? q[(tok0 + tt) * P.q_stride + i] : 0.f;
+        sk[e] = ok ? k[(tok0 + tt) * P.k_stride + i] : 0.f;
+        sg[e] = ok ? g[(tok0 + tt) * g_stride + i] : 0.f;
+      }
+      for (int e = threadIdx.x; e < kDeltaTok * CC; e += 128) {
+        const int tt = e / CC, c = e % CC;
+        sx[e] = (tt < nt && c < vcols) ? to_f32<TV>(v[(tok0 + tt) * P.v_stride + c]) : 0.f;
+      }
+      if (threadIdx.x < kDeltaTok) sb[threadIdx.x] = threadIdx.x < nt ? P.beta[(tok0 + threadIdx.x) * P.H + h] : 0.f;
+      __syncthreads();
+    }
     if (!warp_live) continue;
     float* outp = P.out + tok0 * ((int64_t)P.H * vdim) + (int64_t)h * vdim + col;
     for (int tt = 0; tt < nt; ++tt) {
-      const float4* q4 = reinterpret_cast<const float4*>(sq + tt * KP + ksl * KPT);
-      const float4* k4 = reinterpret_cast<const float4*>(sk + tt * KP + ksl * KPT);
-      const float4* g4 = reinterpret_cast<const float4*>(sg + tt * KP + ksl * KPT);
+      const float4* q4 = reinterpret_cast<const float4*>(sq + b * QK + tt * KP + ksl * KPT);
+      const float4* k4 = reinterpret_cast<const float4*>(sk + b * QK + tt * KP + ksl * KPT);
+      const float4* g4 = reinterpret_cast<const float4*>(sg + b * QK + tt * KP + ksl * KPT);
       float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
       for (int r4 = 0; r4 < KPT / 4; ++r4) {
@@ -108,7 +149,8 @@ delta_rule_kernel(const DeltaParams P) {
       float d = (d0 + d1) + (d2 + d3);
 #pragma unroll
       for (int off = 1; off < NS; off <<= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
-      const float w = sb[tt] * (sx[tt * CC + cl] - d);
+      const float x = VEC ? to_f32<TV>(sxr[(b * kDeltaTok + tt) * CC + cl]) : sx[tt * CC + cl];
+      const float w = sb[b * kDeltaTok + tt] * (x - d);
       float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
       for (int r4 = 0; r4 < KPT / 4; ++r4) {
@@ -140,9 +182,23 @@ delta_rule_kernel(const DeltaParams P) {
 template <typename TV, int KPT, int NS>
 static void delta_launch_as(const DeltaParams& P, int num_seqs, cudaStream_t stream) {
   constexpr int CC = 128 / NS;
+  constexpr int VE = 16 / (int)sizeof(TV);
   const dim3 grid((P.vdim + CC - 1) / CC, P.H, num_seqs);
-  const size_t smem = (size_t)(3 * kDeltaTok * NS * KPT + kDeltaTok * CC + kDeltaTok) * sizeof(float);
-  launch_pdl(delta_rule_kernel<TV, KPT, NS>, grid, dim3(128), smem, stream, P);
+  const bool vec = P.kdim % 4 == 0 && P.q_stride % 4 == 0 && P.k_stride % 4 == 0 && aligned16(P.q) && aligned16(P.k) &&
+                   aligned16(P.g) && P.vdim % VE == 0 && P.v_stride % VE == 0 && aligned16(P.v);
+  if (vec) {
+    const size_t smem = (size_t)2 * (3 * kDeltaTok * NS * KPT + kDeltaTok) * sizeof(float) +
+                        (size_t)2 * kDeltaTok * CC * sizeof(TV);
+    static bool configured = false;                   // one flag per instantiation
+    if (!configured && smem > 48 * 1024) {
+      cudaFuncSetAttribute(delta_rule_kernel<TV, KPT, NS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      configured = true;
+    }
+    launch_pdl(delta_rule_kernel<TV, KPT, NS, true>, grid, dim3(128), smem, stream, P);
+  } else {
+    const size_t smem = (size_t)(3 * kDeltaTok * NS * KPT + kDeltaTok + kDeltaTok * CC) * sizeof(float);
+    launch_pdl(delta_rule_kernel<TV, KPT, NS, false>, grid, dim3(128), smem, stream, P);
+  }
 }
 
 template <typename TV>
