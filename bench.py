@@ -832,6 +832,23 @@ def nirelix_kernel_table(width, head_dim, tokens, seqs, peak_gbs):
         add("attn_generic(latent rows, window 512)", step,
             lambda: ops.attn_generic(qx, cache, None, spans, 0.07, 1, R, block_tables=tables, window=window),
             T * H * (R + dr + R) * 2 + seqs * min(ctx, keys + per) * (R + dr) * 2, flops=att_flops)
+        # what 16-bit prompts and windowed decode steps run instead: library products around the masked softmax kernel
+        from nanovllm.layers.seq_mixers import LatentAttention
+        from nanovllm.utils.context import get_context, reset_context, set_context
+        la = LatentAttention(H, head_dim, dr, head_dim, R, 0.07, window=window)
+        la.k_cache = cache
+        if step == "prompt":
+            set_context(True, cu_seqlens_q=spans.cu_q, cu_seqlens_k=spans.cu_k, max_seqlen_q=per, max_seqlen_k=per,
+                        block_tables=tables, block_size=16, host_spans=[(i * per, per, per) for i in range(seqs)])
+            fn = lambda: la._prefill_by_products(qx, None, get_context(), True)
+            band = sum(min(window, i + 1) for i in range(per)) * seqs          # visible (query, key) pairs
+        else:
+            set_context(False, context_lens=spans.ctx_lens, block_tables=tables, block_size=16)
+            fn = lambda: la._decode_window_by_products(qx, get_context())
+            band = T * keys
+        add("latent attention by products (window 512)", step, fn,
+            T * H * (R + dr + R) * 2 + seqs * min(ctx, keys + per) * (R + dr) * 2, flops=2.0 * band * H * (2 * R + dr))
+        reset_context()
         # mixture of experts: router, then the expert kernels (like: the softmax router and the same expert kernels)
         E, top, ffe = 16, 2, width // 2
         x = rnd(T, width).to(bf)

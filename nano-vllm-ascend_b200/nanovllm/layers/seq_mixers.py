@@ -257,10 +257,13 @@ class LatentAttention(nn.Module):
         rows. Without a window the generic kernel reads the cache through the block table instead."""
         B, H, D = qx.shape
         W, R, bs = self.window, self.rank, ctx.block_size
-        pos = ctx.context_lens.long() - 1                                    # -1 on padded rows
-        j = (pos[:, None] - (W - 1) + torch.arange(W, device=qx.device)).clamp(min=0)
-        blocks = ctx.block_tables.gather(1, j // bs).clamp(min=0).long()
-        rows = self.k_cache.view(-1, D)[(blocks * bs + j % bs).view(-1)].view(B, W, D)
+        slots = ctx.scratch.get(("window rows", W))                          # the same for every layer of the step
+        if slots is None:
+            pos = ctx.context_lens.long() - 1                                # -1 on padded rows
+            j = (pos[:, None] - (W - 1) + torch.arange(W, device=qx.device)).clamp(min=0)
+            blocks = ctx.block_tables.gather(1, j // bs).clamp(min=0).long()
+            slots = ctx.scratch[("window rows", W)] = (blocks * bs + j % bs).view(-1)
+        rows = self.k_cache.view(-1, D)[slots].view(B, W, D)
         if qx.dtype == torch.float32:
             scores = torch.bmm(qx, rows.transpose(1, 2))
         else:
@@ -298,11 +301,12 @@ class LatentAttention(nn.Module):
                 lo = max(0, first + c0 - self.window + 1) if self.window else 0
                 hi = first + c1
                 lo = hi - -(-(hi - lo) // 8) * 8           # a multiple of 8 keys (16-byte rows for the products); a
-                j = torch.arange(lo, hi, device=qx.device).clamp(min=0)     # range that starts before 0 is hidden
-                if paged:
-                    rows = flat[ctx.block_tables[s][j // bs].long() * bs + j % bs]
-                else:                                  # no cache bound: the span's keys are this step's rows
-                    rows = kc[q0 + j]
+                key = ("prompt rows", s, c0, self.window, self.PRODUCT_CHUNK, paged)
+                idx = ctx.scratch.get(key)             # the same for every layer of the step
+                if idx is None:
+                    j = torch.arange(lo, hi, device=qx.device).clamp(min=0)     # a range that starts before 0 is hidden
+                    idx = ctx.scratch[key] = (ctx.block_tables[s][j // bs].long() * bs + j % bs) if paged else q0 + j
+                rows = flat[idx] if paged else kc[idx]     # no cache bound: the span's keys are this step's rows
                 scores = torch.mm(qx[q0 + c0:q0 + c1].reshape(-1, D), rows.t(), out_dtype=torch.float32)
                 p = ops.masked_softmax(scores, H, first + c0, lo, self.scale, self.window, qx.dtype)
                 lat[q0 + c0:q0 + c1] = torch.mm(p, rows[:, :R].contiguous()).view(-1, H * R)

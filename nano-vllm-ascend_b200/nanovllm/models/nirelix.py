@@ -221,6 +221,9 @@ class NirelixForCausalLM(nn.Module):
         return out
 
     def forward(self, input_ids, positions):
+        # index tensors that the layers share live for ONE pass: a context may see several passes (an eager pass, then
+        # the capture of a CUDA graph), and what an earlier pass computed is neither current nor part of the graph
+        get_context().scratch.clear()
         dtype = self.embed_tokens.weight.dtype
         x = self.embed_tokens(input_ids).float()
         T, W = x.shape

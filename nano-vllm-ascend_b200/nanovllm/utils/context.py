@@ -23,11 +23,13 @@ cuBLAS, whose 2-CTA clustered kernels cannot be placed next to a resident attent
 Fourth: ``state_slots`` -- int32 [num_seqs], the state slot of every sequence of the step (hybrid models:
 recurrent state and convolution tails live in per-slot rows; None for models without such state).
 Fifth: ``host_spans`` -- prefill steps: [(first token row, tokens, keys)] per sequence as python ints, for layers
-that launch per sequence (attention composed of library products).
+that launch per sequence (attention composed of library products). Sixth: ``scratch`` -- a dict that lives for
+one pass of the model (the model clears it when a pass starts): index tensors that several layers would otherwise
+recompute (the cache rows of a window).
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 
 import torch
 
@@ -50,6 +52,7 @@ class Context:
     own_gemm: bool = False
     state_slots: torch.Tensor | None = None
     host_spans: list | None = None
+    scratch: dict = field(default_factory=dict)
 
 
 _current = Context()
