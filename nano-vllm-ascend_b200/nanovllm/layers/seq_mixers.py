@@ -237,7 +237,8 @@ class LatentAttention(nn.Module):
         if (ctx.is_prefill and ctx.host_spans is not None and qx.dtype != torch.float32 and not self.force_generic
                 and ctx.max_seqlen_q >= self.PRODUCT_MIN_TOKENS):
             lat = self._prefill_by_products(qx, kc, ctx, paged)
-        elif (not ctx.is_prefill and paged and 0 < self.window <= self.DECODE_WINDOW_MAX and not self.force_generic):
+        elif (not ctx.is_prefill and paged and self.window > 0 and not self.force_generic and
+              min(self.window, ctx.block_tables.shape[1] * ctx.block_size) <= self.DECODE_WINDOW_MAX):
             lat = self._decode_window_by_products(qx, ctx)
         elif paged:
             lat = ops.attn_generic(qx, self.k_cache, None, spans, self.scale, 1, R, block_tables=ctx.block_tables,
@@ -256,7 +257,8 @@ class LatentAttention(nn.Module):
         (rows before a sequence's start and padded graph rows are hidden) and multiplies by the latent part of the same
         rows. Without a window the generic kernel reads the cache through the block table instead."""
         B, H, D = qx.shape
-        W, R, bs = self.window, self.rank, ctx.block_size
+        R, bs = self.rank, ctx.block_size
+        W = min(self.window, ctx.block_tables.shape[1] * bs)                 # no sequence holds more rows than its table
         slots = ctx.scratch.get(("window rows", W))                          # the same for every layer of the step
         if slots is None:
             pos = ctx.context_lens.long() - 1                                # -1 on padded rows
@@ -268,7 +270,8 @@ class LatentAttention(nn.Module):
             scores = torch.bmm(qx, rows.transpose(1, 2))
         else:
             scores = torch.bmm(qx, rows.transpose(1, 2), out_dtype=torch.float32)
-        p = ops.masked_softmax(scores.view(B * H, W), H, 0, 0, self.scale, W, qx.dtype, ctx_lens=ctx.context_lens)
+        p = ops.masked_softmax(scores.view(B * H, W), H, 0, 0, self.scale, self.window, qx.dtype,
+                               ctx_lens=ctx.context_lens)
         return torch.bmm(p.view(B, H, W), rows[:, :, :R]).reshape(B, H * R)
 
     PRODUCT_MIN_TOKENS = 64       # longest portion of the step from which prompts run on library products
