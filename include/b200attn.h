@@ -327,6 +327,12 @@ int b200_moe_gemm_down_umma(void* y, const void* h, const void* w2, const int32_
                             int32_t inter, int32_t hidden, int32_t num_local, int32_t dtype,
                             b200_stream_t stream);
 
+/* Grouped product with fp32 output on the same tcgen05 kernel, the accumulators stored as they are (attention
+ * scores of 16-bit operands): rows offsets[g] .. offsets[g+1] of a [rows, K] are multiplied with w[g] ([groups,
+ * n_out, K]) into out [rows, n_out] fp32. K % 64 == 0, n_out % 128 == 0, groups <= 256. */
+int b200_gemm_f32out_umma(float* out, const void* a, const void* w, const int32_t* offsets, int32_t rows,
+                          int32_t K, int32_t n_out, int32_t groups, int32_t dtype, b200_stream_t stream);
+
 /* ---------------------------------------------------------------------------------
  * C1 (fused)  tensor-parallel all-reduce + residual add + RMSNorm in one kernel over NVLink peer
  * memory, for decode-sized messages.
@@ -535,9 +541,11 @@ int b200_latent_kv_prep(void* cq, void* kc, void* cache, const int32_t* slots, i
  * key_lo + j. ctx_lens given (int32 per sequence): row r belongs to sequence r / heads, whose token is at position
  * ctx_lens[.] - 1 (0: padded row, zeros), column j the key at position pos - nk + 1 + j. A key at position kp is
  * visible iff 0 <= kp <= pos and (window == 0 or kp > pos - window). p [rows, nk] (dtype) = softmax(scale s) over
- * the visible keys, 0 elsewhere. scale > 0. */
+ * the visible keys, 0 elsewhere. scale > 0. chunk_first / chunk_lo (int32 per chunk of rows_per_chunk rows): chunk c
+ * holds consecutive tokens from position chunk_first[c] on against keys from position chunk_lo[c] on. */
 int b200_masked_softmax(void* p, const float* s, int64_t rows, int32_t nk, int32_t heads, int32_t first_pos,
-                        int32_t key_lo, int32_t window, float scale, const int32_t* ctx_lens, int32_t dtype,
+                        int32_t key_lo, int32_t window, float scale, const int32_t* ctx_lens,
+                        const int32_t* chunk_first, const int32_t* chunk_lo, int32_t rows_per_chunk, int32_t dtype,
                         b200_stream_t stream);
 
 /* out[r, i] = g sigmoid(alpha g) (u + 1), g = min(x[r, i], limit), u = clamp(x[r, inter + i], -limit, limit). */

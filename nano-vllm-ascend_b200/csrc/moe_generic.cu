@@ -53,7 +53,7 @@ moe_route_grouped_kernel(int32_t* __restrict__ ids, float* __restrict__ weights,
       gs[i] = g < groups ? (per > 1 ? a + b : a) : -INFINITY;
     }
     unsigned kept[(kRouteMaxGroups + 31) / 32] = {0u, 0u};   // bit `lane` of word i: group lane + 32 i is kept
-    for (int round = 0; round < keep; ++round) {
+    for (int pick = 0; pick < keep; ++pick) {
       float best = -INFINITY;
       int arg = 0x7fffffff;
 #pragma unroll

@@ -30,6 +30,7 @@ struct MoeUmmaParams {
   const void* pair_scale;      // down: routing weight per pair
   void* out;                   // gate_up: H [pairs, n_out]; down: Y [pairs, n_out]
   int num_local, K, n_out;
+  int out_f32;                 // plain epilogue only: the fp32 accumulators are stored as they are (out is float*)
 };
 
 // Ring depth: 3 stages (97 KB, two CTAs per SM) for tensor-bound grouped GEMMs, where the second CTA's
@@ -179,7 +180,12 @@ moe_umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         uint32_t a[32];
         umma::ld32(tb + lane_base + c0, a);
         umma::wait_ld();
-        if (valid) {
+        if (valid && p.out_f32) {                    // attention scores: no rounding between the product and the softmax
+          float* orow32 = reinterpret_cast<float*>(p.out) + pos * p.n_out + n0 + c0;
+#pragma unroll
+          for (int c = 0; c < 32; c += 4)
+            *reinterpret_cast<uint4*>(orow32 + c) = make_uint4(a[c], a[c + 1], a[c + 2], a[c + 3]);
+        } else if (valid) {
 #pragma unroll
           for (int c = 0; c < 32; c += 8) {
             uint32_t w[4];
@@ -277,7 +283,8 @@ extern "C" int b200_moe_gather_rows(void* xs, const void* x, const int32_t* offs
 
 static int moe_umma_common(bool gate_up, void* out, const void* a, const void* w, const int32_t* offsets,
                            const int32_t* sorted_pair, const void* pair_scale, int32_t pairs, int32_t K,
-                           int32_t n_out, int32_t num_local, int32_t dtype, b200_stream_t stream) {
+                           int32_t n_out, int32_t num_local, int32_t dtype, b200_stream_t stream,
+                           int out_f32 = 0) {
   B200_RETURN_IF(dtype != B200_DTYPE_BF16 && dtype != B200_DTYPE_F16, B200_ERR_BAD_DTYPE);
   B200_RETURN_IF(pairs < 0 || K <= 0 || n_out <= 0 || num_local <= 0, B200_ERR_BAD_SHAPE);
   B200_RETURN_IF(K % 64 != 0 || n_out % (gate_up ? 64 : 128) != 0 || num_local > 256, B200_ERR_UNSUPPORTED);
@@ -291,7 +298,7 @@ static int moe_umma_common(bool gate_up, void* out, const void* a, const void* w
   const int64_t w_rows = (int64_t)num_local * (gate_up ? 2 : 1) * n_out;
   rc = get_panel_map(w, w_rows, (int64_t)K * 2, K / 64, 64, 1, dtype, &mw);
   if (rc != B200_OK) return rc;
-  MoeUmmaParams p{offsets, sorted_pair, pair_scale, out, num_local, K, n_out};
+  MoeUmmaParams p{offsets, sorted_pair, pair_scale, out, num_local, K, n_out, out_f32};
   return dtype == B200_DTYPE_BF16 ? moe_umma_launch<__nv_bfloat16>(gate_up, ma, mw, p, pairs, (cudaStream_t)stream)
                                   : moe_umma_launch<__half>(gate_up, ma, mw, p, pairs, (cudaStream_t)stream);
 }
@@ -309,4 +316,10 @@ extern "C" int b200_moe_gemm_down_umma(void* y, const void* h, const void* w2, c
                                        b200_stream_t stream) {
   return moe_umma_common(false, y, h, w2, offsets, sorted_pair, topk_weights, pairs, inter, hidden, num_local,
                          dtype, stream);
+}
+
+extern "C" int b200_gemm_f32out_umma(float* out, const void* a, const void* w, const int32_t* offsets,
+                                     int32_t rows, int32_t K, int32_t n_out, int32_t groups, int32_t dtype,
+                                     b200_stream_t stream) {
+  return moe_umma_common(false, out, a, w, offsets, nullptr, nullptr, rows, K, n_out, groups, dtype, stream, 1);
 }

@@ -380,18 +380,25 @@ glu_clamped_vec_kernel(T* __restrict__ out, const T* __restrict__ x, int64_t row
 //   ctx_lens != nullptr: row r belongs to sequence r / heads, whose one token sits at position ctx_lens[.] - 1 (0 keys:
 //                        a padded row, all zeros), and column j is the key at position pos - nk + 1 + j (the last nk
 //                        positions, gathered by the caller; negative positions do not exist).
+//   chunk_first != nullptr: the rows come in chunks of rows_per_chunk; chunk c holds consecutive tokens of one sequence
+//                        from position chunk_first[c] on, against keys from position chunk_lo[c] on (may be negative).
 // A key at position kp is visible iff 0 <= kp <= pos and (window == 0 or kp > pos - window). p = softmax(scale * s)
 // over the visible keys, written in the element type; hidden keys get 0.
 template <typename T>
 __global__ void __launch_bounds__(128)
 masked_softmax_kernel(T* __restrict__ p, const float* __restrict__ s, int64_t rows, int nk, int heads, int first_pos,
-                      int key_lo, int window, float scale, const int* __restrict__ ctx_lens) {
+                      int key_lo, int window, float scale, const int* __restrict__ ctx_lens,
+                      const int* __restrict__ chunk_first, const int* __restrict__ chunk_lo, int rows_per_chunk) {
   pdl_wait();
   const int lane = threadIdx.x & 31;
   const int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (r >= rows) return;
   int pos = first_pos + (int)(r / heads);
-  if (ctx_lens != nullptr) {
+  if (chunk_first != nullptr) {
+    const int64_t c = r / rows_per_chunk;
+    pos = chunk_first[c] + (int)((r % rows_per_chunk) / heads);
+    key_lo = chunk_lo[c];
+  } else if (ctx_lens != nullptr) {
     pos = ctx_lens[r / heads] - 1;
     key_lo = pos - nk + 1;
   }
@@ -417,14 +424,15 @@ using namespace b200;
 
 extern "C" int b200_masked_softmax(void* p, const float* s, int64_t rows, int32_t nk, int32_t heads,
                                    int32_t first_pos, int32_t key_lo, int32_t window, float scale,
-                                   const int32_t* ctx_lens, int32_t dtype, b200_stream_t stream) {
+                                   const int32_t* ctx_lens, const int32_t* chunk_first, const int32_t* chunk_lo,
+                                   int32_t rows_per_chunk, int32_t dtype, b200_stream_t stream) {
   B200_RETURN_IF(rows < 0 || nk <= 0 || heads <= 0 || first_pos < 0 || window < 0 || scale <= 0.f,
                  B200_ERR_BAD_SHAPE);
   if (rows == 0) return B200_OK;
-  B200_RETURN_IF(!p || !s, B200_ERR_NULL_POINTER);
+  B200_RETURN_IF(!p || !s || (chunk_first && (!chunk_lo || rows_per_chunk <= 0)), B200_ERR_NULL_POINTER);
   B200_DISPATCH_3(dtype, T, launch_pdl(masked_softmax_kernel<T>, dim3((unsigned)((rows + 3) / 4)), dim3(128), 0,
                                        (cudaStream_t)stream, (T*)p, s, rows, nk, heads, first_pos, key_lo, window,
-                                       scale, ctx_lens));
+                                       scale, ctx_lens, chunk_first, chunk_lo, rows_per_chunk));
   return finish_launch();
 }
 

@@ -74,6 +74,8 @@ PROTOTYPES = {
                                        c_int32, c_int64, c_int32, c_void_p]),
     "b200_moe_gemm_gate_up_umma": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32,
                                              c_int32, c_int32, c_int32, c_void_p]),
+    "b200_gemm_f32out_umma": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32, c_int32,
+                                        c_int32, c_void_p]),
     "b200_moe_gemm_down_umma": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                           c_int32, c_int32, c_int32, c_int32, c_int32, c_void_p]),
     "b200_moe_combine": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,
@@ -136,7 +138,7 @@ PROTOTYPES = {
                                       c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_int32,
                                       c_int32, c_int32, c_double, c_int32, c_float, c_int32, c_void_p]),
     "b200_masked_softmax": (c_int32, [c_void_p, c_void_p, c_int64, c_int32, c_int32, c_int32, c_int32, c_int32,
-                                      c_float, c_void_p, c_int32, c_void_p]),
+                                      c_float, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_void_p]),
     "b200_glu_clamped": (c_int32, [c_void_p, c_void_p, c_int32, c_int32, c_float, c_float, c_int32, c_void_p]),
     "b200_moe_route_grouped": (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int32, c_int32,
                                          c_int32, c_int32, c_int32, c_float, c_void_p]),

@@ -274,45 +274,117 @@ class LatentAttention(nn.Module):
                                ctx_lens=ctx.context_lens)
         return torch.bmm(p.view(B, H, W), rows[:, :, :R]).reshape(B, H * R)
 
+    OWN_SCORE_PRODUCT = True      # scores on the tcgen05 GEMM of csrc/moe_umma.cu (False: torch.bmm with fp32 output)
+    PRODUCT_BYTES = 512 << 20     # fp32 scores held at a time
     PRODUCT_MIN_TOKENS = 64       # longest portion of the step from which prompts run on library products
     PRODUCT_CHUNK = 512           # query tokens per product
 
-    def _prefill_by_products(self, qx, kc, ctx, paged):
-        """Prompt portions of 16-bit models on the tensor cores: per sequence and per chunk of query tokens, the
-        scores of all heads against the chunk's visible key range as ONE library product with fp32 output (all
-        heads share the latent rows), the masked softmax kernel (fp32 in, 16-bit probabilities out), and one
-        product with the latent part of the same rows. Short portions and fp32 models run on attn_generic."""
-        T, H, R = qx.shape[0], self.num_heads, self.rank
-        D = R + self.rot
-        lat = torch.empty(T, H * R, dtype=qx.dtype, device=qx.device)
-        bs = ctx.block_size
-        flat = self.k_cache.view(-1, D) if paged else None
+    def _prompt_plan(self, ctx, paged, device):
+        """Index tensors of the step's prompt chunks, built once per pass and shared by the layers: every span of at
+        least PRODUCT_MIN_TOKENS tokens is cut into chunks of PRODUCT_CHUNK query tokens; all chunks see a key range of
+        the same length NK (a multiple of 128 that covers the widest visible range; what lies before a sequence's
+        start or outside a row's window is hidden by the softmax kernel)."""
+        import numpy as np
+        CH, W, bs = self.PRODUCT_CHUNK, self.window, ctx.block_size
+        chunks, short = [], []                      # (sequence, first token row, tokens, first position)
         for s, (q0, ql, kl) in enumerate(ctx.host_spans):
-            first = kl - ql
-            if ql < self.PRODUCT_MIN_TOKENS:          # a short portion or a single token beside long ones
-                sub = ops.StepSpans(torch.tensor([0, ql], dtype=torch.int32, device=qx.device),
-                                    torch.tensor([0, kl], dtype=torch.int32, device=qx.device), None, ql)
-                if paged:
-                    lat[q0:q0 + ql] = ops.attn_generic(qx[q0:q0 + ql], self.k_cache, None, sub, self.scale, 1, R,
-                                                       block_tables=ctx.block_tables[s:s + 1], window=self.window)
-                else:
-                    lat[q0:q0 + ql] = ops.attn_generic(qx[q0:q0 + ql], kc[q0:q0 + ql].unsqueeze(1), None, sub,
-                                                       self.scale, 1, R, window=self.window)
+            if ql < self.PRODUCT_MIN_TOKENS:
+                short.append((s, q0, ql, kl))
                 continue
-            for c0 in range(0, ql, self.PRODUCT_CHUNK):
-                c1 = min(ql, c0 + self.PRODUCT_CHUNK)
-                lo = max(0, first + c0 - self.window + 1) if self.window else 0
-                hi = first + c1
-                lo = hi - -(-(hi - lo) // 8) * 8           # a multiple of 8 keys (16-byte rows for the products); a
-                key = ("prompt rows", s, c0, self.window, self.PRODUCT_CHUNK, paged)
-                idx = ctx.scratch.get(key)             # the same for every layer of the step
-                if idx is None:
-                    j = torch.arange(lo, hi, device=qx.device).clamp(min=0)     # a range that starts before 0 is hidden
-                    idx = ctx.scratch[key] = (ctx.block_tables[s][j // bs].long() * bs + j % bs) if paged else q0 + j
-                rows = flat[idx] if paged else kc[idx]     # no cache bound: the span's keys are this step's rows
-                scores = torch.mm(qx[q0 + c0:q0 + c1].reshape(-1, D), rows.t(), out_dtype=torch.float32)
-                p = ops.masked_softmax(scores, H, first + c0, lo, self.scale, self.window, qx.dtype)
-                lat[q0 + c0:q0 + c1] = torch.mm(p, rows[:, :R].contiguous()).view(-1, H * R)
+            for c0 in range(0, ql, CH):
+                chunks.append((s, q0 + c0, min(CH, ql - c0), kl - ql + c0))
+        plan = {"short": short, "chunks": len(chunks)}
+        if not chunks:
+            return plan
+        seq = np.array([c[0] for c in chunks])
+        row0 = np.array([c[1] for c in chunks])
+        n = np.array([c[2] for c in chunks])
+        pos0 = np.array([c[3] for c in chunks])
+        hi = pos0 + n                                # keys of a chunk end at its last token
+        vis_lo = np.maximum(0, pos0 - W + 1) if W else np.zeros_like(pos0)
+        NK = int(-(-int((hi - vis_lo).max()) // 128) * 128)
+        lo = hi - NK                                 # may be negative: those columns repeat row 0 and are hidden
+        dev = lambda a, dt: torch.from_numpy(np.ascontiguousarray(a)).to(dt).to(device, non_blocking=True)
+        tok = np.arange(CH)[None, :]
+        qrows = row0[:, None] + np.minimum(tok, n[:, None] - 1)           # rows past a chunk's end repeat its last token
+        kpos = np.maximum(lo[:, None] + np.arange(NK)[None, :], 0)
+        kpos_d = dev(kpos, torch.int64)
+        if paged:
+            tables = ctx.block_tables[dev(seq, torch.int64)]               # [chunks, blocks]
+            kslots = tables.gather(1, kpos_d // bs).long() * bs + kpos_d % bs
+        else:                                        # no cache bound: a span's keys are this step's rows
+            span_row0 = np.array([ctx.host_spans[c[0]][0] for c in chunks])
+            kslots = kpos_d + dev(span_row0, torch.int64)[:, None]
+        valid = tok < n[:, None]                     # [chunks, CH]
+        flatq = qrows.reshape(-1)
+        # chunks that are all full and follow each other in the packed batch need no gather of query rows
+        plan["run"] = int(flatq[0]) if bool(valid.all()) and bool((np.diff(flatq) == 1).all()) else None
+        plan.update(NK=NK, qrows=dev(qrows.reshape(-1), torch.int64), kslots=kslots.reshape(-1),
+                    first=dev(pos0, torch.int32), lo=dev(lo, torch.int32),
+                    src=dev(np.nonzero(valid.reshape(-1))[0], torch.int64), dst=dev(qrows[valid], torch.int64),
+                    full=bool(valid.all()))
+        return plan
+
+    def _prefill_by_products(self, qx, kc, ctx, paged):
+        """Prompt portions of 16-bit models on the tensor cores, all chunks of the step at once: gather the chunks'
+        query rows and key ranges; scores of ALL heads of a chunk against its key range as one group of a grouped
+        product with fp32 output (the heads share the latent rows; the library's tcgen05 GEMM of csrc/moe_umma.cu, or
+        torch.bmm with fp32 output); the masked softmax kernel (fp32 in, 16-bit probabilities out); one batched product
+        with the latent part of the same rows. Portions shorter than PRODUCT_MIN_TOKENS beside long ones, and fp32
+        models, run on attn_generic."""
+        T, H, R = qx.shape[0], self.num_heads, self.rank
+        D, CH = R + self.rot, self.PRODUCT_CHUNK
+        key = ("prompt plan", self.window, CH, self.PRODUCT_MIN_TOKENS, paged)
+        plan = ctx.scratch.get(key)
+        if plan is None:
+            plan = ctx.scratch[key] = self._prompt_plan(ctx, paged, qx.device)
+        lat = torch.empty(T, H * R, dtype=qx.dtype, device=qx.device)
+        for s, q0, ql, kl in plan["short"]:
+            sub = ops.StepSpans(torch.tensor([0, ql], dtype=torch.int32, device=qx.device),
+                                torch.tensor([0, kl], dtype=torch.int32, device=qx.device), None, ql)
+            if paged:
+                lat[q0:q0 + ql] = ops.attn_generic(qx[q0:q0 + ql], self.k_cache, None, sub, self.scale, 1, R,
+                                                   block_tables=ctx.block_tables[s:s + 1], window=self.window)
+            else:
+                lat[q0:q0 + ql] = ops.attn_generic(qx[q0:q0 + ql], kc[q0:q0 + ql].unsqueeze(1), None, sub,
+                                                   self.scale, 1, R, window=self.window)
+        NC = plan["chunks"]
+        if NC == 0:
+            return lat
+        NK = plan["NK"]
+        # the tcgen05 GEMM multiplies 64 columns at a time; rows of other widths would have to be copied into padded
+        # buffers (measured slower than the library's product at 288 columns), except where they are tiny
+        own = self.OWN_SCORE_PRODUCT and (D % 64 == 0 or D < 64)
+        Dp = -(-D // 64) * 64 if own else D
+        flat = self.k_cache.view(-1, D) if paged else kc
+        per = max(1, min(256, self.PRODUCT_BYTES // (CH * H * NK * 4)))      # chunks per launch: bounded score memory
+        for g0 in range(0, NC, per):
+            g1 = min(NC, g0 + per)
+            G = g1 - g0
+            rows = flat[plan["kslots"][g0 * NK:g1 * NK]]                           # [G * NK, D]
+            run = plan["run"]
+            q = (qx[run + g0 * CH:run + g1 * CH] if run is not None else qx[plan["qrows"][g0 * CH:g1 * CH]]).reshape(
+                G * CH * H, D)
+            if own:
+                if Dp != D:
+                    rows_p, q = torch.nn.functional.pad(rows, (0, Dp - D)), torch.nn.functional.pad(q, (0, Dp - D))
+                else:
+                    rows_p = rows
+                offsets = torch.arange(0, (G + 1) * CH * H, CH * H, dtype=torch.int32, device=qx.device)
+                scores = ops.scores_umma(q, rows_p.view(G, NK, Dp), offsets)       # [G * CH * H, NK] fp32
+            else:
+                scores = torch.bmm(q.view(G, CH * H, D), rows.view(G, NK, D).transpose(1, 2),
+                                   out_dtype=torch.float32).view(G * CH * H, NK)
+            p = ops.masked_softmax(scores, H, 0, 0, self.scale, self.window, qx.dtype,
+                                   chunks=(plan["first"][g0:g1], plan["lo"][g0:g1], CH * H))
+            out = torch.bmm(p.view(G, CH * H, NK), rows.view(G, NK, D)[:, :, :R].contiguous()).view(G * CH, H * R)
+            if run is not None:
+                lat[run + g0 * CH:run + g1 * CH] = out
+            elif plan["full"]:
+                lat[plan["qrows"][g0 * CH:g1 * CH]] = out
+            else:
+                sel = (plan["src"] >= g0 * CH) & (plan["src"] < g1 * CH)
+                lat[plan["dst"][sel]] = out[plan["src"][sel] - g0 * CH]
         return lat
 
 

@@ -414,6 +414,26 @@ def linear_umma(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = Non
     return out
 
 
+def scores_umma(x: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor | None = None) -> torch.Tensor:
+    """Products with fp32 OUTPUT on the tcgen05 kernel (the accumulators are stored unrounded): attention scores of
+    16-bit operands. x [M, K] @ w [N, K]^T, or grouped: w [G, N, K] and offsets int32 [G + 1], rows offsets[g] ..
+    offsets[g+1] of x against w[g]. Contiguous; K % 64 == 0, N % 128 == 0, G <= 256. Returns fp32 [M, N]."""
+    _need_cuda(x, w, offsets)
+    M, K = x.shape
+    G = w.shape[0] if w.dim() == 3 else 1
+    N = w.shape[-2]
+    if not x.is_contiguous() or not w.is_contiguous() or w.shape[-1] != K or x.dtype != w.dtype:
+        raise ValueError("scores_umma takes contiguous x [M, K] and w [(G,) N, K] of one 16-bit dtype")
+    if (offsets is None) != (w.dim() == 2) or (offsets is not None and (offsets.dtype != torch.int32 or
+                                                                        offsets.numel() != G + 1)):
+        raise ValueError("grouped form: w [G, N, K] with int32 offsets [G + 1]")
+    out = torch.empty(M, N, dtype=torch.float32, device=x.device)
+    off = offsets if offsets is not None else _dense_plan(M, x.device)
+    _C.check(_C.load().b200_gemm_f32out_umma(out.data_ptr(), x.data_ptr(), w.data_ptr(), off.data_ptr(), M, K, N, G,
+                                             _dt(x), _stream()), "b200_gemm_f32out_umma")
+    return out
+
+
 # ------------------------------------------------------------------ sparse MoE (csrc/moe.cu)
 class MoePlan:
     """Device-side dispatch plan of one MoE layer call (b200_moe_align): fixed-capacity buffers,
@@ -904,22 +924,31 @@ def latent_kv_prep(dq, dkv, wq, wc, positions, rank, rot, dims, base, interleave
     return cq, kc
 
 
-def masked_softmax(scores, heads, first_pos, key_lo, scale, window, dtype, ctx_lens=None):
+def masked_softmax(scores, heads, first_pos, key_lo, scale, window, dtype, ctx_lens=None, chunks=None):
     """scores fp32 [rows, nk] of `heads` query heads per token -> softmax(scale * scores) over the visible keys in
-    `dtype`, hidden keys 0. Without ctx_lens the rows are consecutive tokens of one sequence (row r at position
+    `dtype`, hidden keys 0. Without ctx_lens / chunks the rows are consecutive tokens of one sequence (row r at position
     first_pos + r // heads, column j the key at position key_lo + j); with ctx_lens (int32 per sequence) row r is the
-    one token of sequence r // heads at position ctx_lens - 1 and column j the key at position pos - nk + 1 + j. A key
-    is visible iff it exists, is not ahead of the token and lies inside the window (0: no window)."""
+    one token of sequence r // heads at position ctx_lens - 1 and column j the key at position pos - nk + 1 + j; with
+    chunks = (first int32 [C], lo int32 [C], rows_per_chunk) chunk c holds consecutive tokens from position first[c]
+    on against keys from position lo[c] on. A key is visible iff it exists, is not ahead of the token and lies inside
+    the window (0: no window)."""
     _need_cuda(scores, ctx_lens)
     if scores.dtype != torch.float32 or not scores.is_contiguous() or scores.dim() != 2:
         raise TypeError("scores are a contiguous fp32 matrix")
     if ctx_lens is not None and (ctx_lens.dtype != torch.int32 or not ctx_lens.is_contiguous()):
         raise TypeError("ctx_lens must be contiguous int32")
     rows, nk = scores.shape
+    cf = cl = None
+    per = 0
+    if chunks is not None:
+        cf, cl, per = chunks
+        _need_cuda(cf, cl)
+        if cf.dtype != torch.int32 or cl.dtype != torch.int32 or cf.numel() * per != rows or cl.numel() != cf.numel():
+            raise TypeError("chunks: int32 first / lo per chunk, rows_per_chunk * chunks == rows")
     p = torch.empty(rows, nk, dtype=dtype, device=scores.device)
     _C.check(_C.load().b200_masked_softmax(p.data_ptr(), scores.data_ptr(), rows, nk, int(heads), int(first_pos),
-                                           int(key_lo), int(window), float(scale), _ptr(ctx_lens), _DT3[dtype],
-                                           _stream()), "b200_masked_softmax")
+                                           int(key_lo), int(window), float(scale), _ptr(ctx_lens), _ptr(cf), _ptr(cl),
+                                           int(per), _DT3[dtype], _stream()), "b200_masked_softmax")
     return p
 
 

@@ -674,11 +674,13 @@ def test_latent_rows_norms_rotation_and_cache_write():
         assert torch.allclose(cache.view(64, -1)[flat.long()].cpu().to(F64), want, atol=1e-5)
 
 
-def test_latent_prompts_on_library_products():
+@pytest.mark.parametrize("own", [True, False])
+def test_latent_prompts_on_library_products(own):
     """Prompt portions of a 16-bit model run as library products around the masked softmax kernel: a 150-token
     portion that continues 60 cached tokens (three query chunks of 64, key ranges that start inside the window), a
     second whole sequence, and a short portion beside them, over a shuffled block table; same loud key at the
-    window's edge as in the kernel's own test."""
+    window's edge as in the kernel's own test. `own`: the scores on the tcgen05 GEMM with fp32 output (key ranges of
+    128 rows, rows padded from 40 to 64 columns) or on the library's mixed-precision product."""
     from nanovllm import ops
     from nanovllm.layers.seq_mixers import LatentAttention
     from nanovllm.utils.context import reset_context, set_context
@@ -689,6 +691,7 @@ def test_latent_prompts_on_library_products():
     attn = LatentAttention(H, dim - rank - 4, 4 + 0, 8, rank, 0.5, window=window)      # sizes only matter as rank + rot = 40
     attn.rot = dim - rank
     attn.PRODUCT_CHUNK = 64
+    attn.OWN_SCORE_PRODUCT = own
     nb = sum(-(-n // bs) for n in lens)
     order = list(range(nb))
     random.Random(3).shuffle(order)
