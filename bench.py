@@ -828,7 +828,7 @@ def nirelix_kernel_table(width, head_dim, tokens, seqs, peak_gbs):
             T * ((Q + R + dr) * 2 + Q * 2 + 2 * (R + dr) * 2))
         qx = (rnd(T, H, R + dr) * 0.3).to(bf)
         keys = min(window, ctx)
-        att_flops = 2.0 * T * H * (min(window, (per + 1) / 2 + 0) if step == "prompt" else keys) * (2 * R + dr)
+        att_flops = 2.0 * T * H * (min(window, (per + 1) / 2) if step == "prompt" else keys) * (2 * R + dr)
         add("attn_generic(latent rows, window 512)", step,
             lambda: ops.attn_generic(qx, cache, None, spans, 0.07, 1, R, block_tables=tables, window=window),
             T * H * (R + dr + R) * 2 + seqs * min(ctx, keys + per) * (R + dr) * 2, flops=att_flops)

@@ -193,6 +193,7 @@ struct RotaryParams {
   int in_head, out_head;
   const int64_t* positions;
   int tokens, heads, width, dims, interleaved, split, out_f32;
+  int hsplit;                 // threads per (token, pair): each takes every hsplit-th head (few tokens: more threads)
   float scale_lo, scale_hi;   // heads < split are multiplied by scale_lo, the others by scale_hi
   double log2_base;
 };
@@ -203,9 +204,11 @@ rotary_heads_kernel(const RotaryParams P) {
   pdl_wait();
   const int half = P.dims / 2;
   const int per_tok = half + (P.width - P.dims);      // work items per token: pairs, then pass-through columns
-  const int64_t total = (int64_t)P.tokens * per_tok;
+  const int64_t total = (int64_t)P.tokens * per_tok * P.hsplit;
   for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
-    const int t = (int)(e / per_tok), w = (int)(e % per_tok);
+    const int h0 = (int)(e % P.hsplit);
+    const int64_t item = e / P.hsplit;
+    const int t = (int)(item / per_tok), w = (int)(item % per_tok);
     const T* src = (const T*)P.in + (int64_t)t * P.in_stride;
     float* of = (float*)P.out + (int64_t)t * P.out_stride;
     T* ot = (T*)P.out + (int64_t)t * P.out_stride;
@@ -215,7 +218,7 @@ rotary_heads_kernel(const RotaryParams P) {
       sincos((double)P.positions[t] * f, &sn, &cs);
       const float c = (float)cs, s = (float)sn;
       const int a = P.interleaved ? 2 * w : w, b = P.interleaved ? 2 * w + 1 : w + half;
-      for (int hd = 0; hd < P.heads; ++hd) {
+      for (int hd = h0; hd < P.heads; hd += P.hsplit) {
         const float sc = hd < P.split ? P.scale_lo : P.scale_hi;
         const float u = to_f32<T>(src[(int64_t)hd * P.in_head + a]), v = to_f32<T>(src[(int64_t)hd * P.in_head + b]);
         const float ra = (u * c - v * s) * sc, rb = (v * c + u * s) * sc;
@@ -229,7 +232,7 @@ rotary_heads_kernel(const RotaryParams P) {
       }
     } else {
       const int col = P.dims + (w - half);
-      for (int hd = 0; hd < P.heads; ++hd) {
+      for (int hd = h0; hd < P.heads; hd += P.hsplit) {
         const float sc = hd < P.split ? P.scale_lo : P.scale_hi;
         const float u = to_f32<T>(src[(int64_t)hd * P.in_head + col]) * sc;
         if (P.out_f32) of[(int64_t)hd * P.out_head + col] = u;
@@ -490,7 +493,12 @@ extern "C" int b200_rotary_heads(void* out, int64_t out_stride, int32_t out_head
   P.out_head = out_head, P.positions = positions, P.tokens = tokens, P.heads = heads, P.width = width;
   P.dims = dims, P.interleaved = interleaved, P.split = split, P.out_f32 = out_f32, P.scale_lo = scale_lo;
   P.scale_hi = scale_hi, P.log2_base = log2(base);
-  const int64_t total = (int64_t)tokens * (dims / 2 + (width - dims));
+  const int64_t items = (int64_t)tokens * (dims / 2 + (width - dims));
+  int64_t hsplit = items > 0 ? 32768 / items : 1;     // a decode step has few (token, pair) items: split the heads too
+  if (hsplit < 1) hsplit = 1;
+  if (hsplit > heads) hsplit = heads;
+  P.hsplit = (int)hsplit;
+  const int64_t total = items * hsplit;
   int grid = (int)((total + 255) / 256);
   if (grid > 148 * 16) grid = 148 * 16;
   B200_DISPATCH_3(dtype, T, launch_pdl(rotary_heads_kernel<T>, dim3(grid), dim3(256), 0, (cudaStream_t)stream, P));
